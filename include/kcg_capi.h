@@ -1,0 +1,145 @@
+/*
+ * kcg_capi.h -- C-ABI launch layer of the B200 (sm_100a) backend.
+ *
+ * The reference project (yao-jiashu/KernelCodeGen) has no FFI of its own: its Backend returns
+ * CUDA source text (src/Backend/CUDA.cc:878-890) whose kernels take flat row-major device
+ * pointers in first-touch order -- (A, B, C) for matmul, (Q, K, V, O) for attention
+ * (src/Backend/CUDA.cc:217-266, 795-801) -- and an out-of-tree harness compiled and launched
+ * that text (test/test.cc:26-34).  The entry points below take the place of that
+ * "emit text, compile, launch" step: same pointer order, same row-major layouts, but the
+ * kernels are hand-written for sm_100a and are launched directly.
+ *
+ * Conventions
+ *   - every pointer is caller-owned DEVICE memory unless the name says host;
+ *   - launches are asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default);
+ *   - nothing here allocates device memory unless documented; scratch is passed in;
+ *   - no exceptions cross this boundary; every call returns a kcg_status_t;
+ *   - there is no CPU fallback: without an sm_100 device the launch calls fail with
+ *     KCG_UNSUPPORTED / KCG_CUDA_ERROR.
+ */
+#ifndef KCG_CAPI_H_
+#define KCG_CAPI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum kcg_status_t {
+  KCG_OK = 0,
+  KCG_BAD_SHAPE = 1,      /* non-positive extent, K mismatch, head_dim not supported ...   */
+  KCG_BAD_ALIGN = 2,      /* pointer not 16-byte aligned or leading dimension not 16 bytes  */
+  KCG_UNSUPPORTED = 3,    /* dtype / precision / tile combination with no kernel            */
+  KCG_CUDA_ERROR = 4,     /* a CUDA runtime/driver call failed                              */
+  KCG_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (see kcg_last_device_status)*/
+  KCG_PEER_TIMEOUT = 6,   /* host-side check-in of the ranks timed out                      */
+  KCG_NCCL_ERROR = 7,
+  KCG_BAD_WORKSPACE = 8,  /* workspace NULL or smaller than kcg_*_workspace_bytes()         */
+  KCG_BAD_ARGUMENT = 9    /* NULL descriptor / NULL tensor pointer                          */
+} kcg_status_t;
+
+typedef enum kcg_dtype_t { KCG_F32 = 0, KCG_BF16 = 1 } kcg_dtype_t;
+
+/* How an fp32 contraction is carried out on the tensor cores.
+ *   3XTF32: a = a_hi + a_lo, C = a_lo*b_hi + a_hi*b_lo + a_hi*b_hi, fp32 accumulate --
+ *           keeps the reference's fp32 contract (src/Frontend/Operators.cc:163-164) to ~1e-6.
+ *   TF32  : one TF32 product (10-bit mantissa inputs).
+ *   BF16  : inputs are bf16 in memory. */
+typedef enum kcg_precision_t {
+  KCG_PREC_3XTF32 = 0,
+  KCG_PREC_TF32 = 1,
+  KCG_PREC_BF16 = 2
+} kcg_precision_t;
+
+typedef enum kcg_epilogue_t { KCG_EPI_NONE = 0, KCG_EPI_RELU = 1 } kcg_epilogue_t;
+
+/* Layout of the B operand, named after the reference's enum Layout (include/enum.h:24-27):
+ * ROW_MAJOR = B stored [K, N]; COL_MAJOR = B stored [N, K] (the QK^T case,
+ * src/Frontend/Operators.cc:301-307). A and C are always row-major. */
+typedef enum kcg_layout_t { KCG_ROW_MAJOR = 0, KCG_COL_MAJOR = 1 } kcg_layout_t;
+
+/* C[M,N] = epilogue(A[M,K] . B), replaces the kernel generated from Matmul::build
+ * (src/Frontend/Operators.cc:77-179) + Relu::build (:182-250) by MatmulOptimizer
+ * (src/Optimizer/Optimizer.cc:383-548).  Leading dimensions are in ELEMENTS.
+ * tile_n / stages / group_m are the schedule knobs (0 = library default):
+ *   tile_n  <- BLOCK_SIZE_N (128 or 256),  tile_m is fixed at 128 (one UMMA M),
+ *   stages  <- depth of the TMA->UMMA shared-memory ring,
+ *   group_m <- GROUP_SIZE_M: how many row-blocks are walked before moving to the next
+ *              column-block (L2 reuse of the B panel). */
+typedef struct kcg_gemm_desc {
+  int64_t M, N, K;
+  int64_t lda, ldb, ldc;
+  int32_t dtype_in;  /* kcg_dtype_t of A and B  */
+  int32_t dtype_out; /* kcg_dtype_t of C        */
+  int32_t precision; /* kcg_precision_t         */
+  int32_t epilogue;  /* kcg_epilogue_t          */
+  int32_t b_layout;  /* kcg_layout_t            */
+  int32_t tile_n;
+  int32_t stages;
+  int32_t group_m;
+  /* Fused all-gather (optional): when n_peers > 0 every finished C tile is also stored to
+   * peer_c[i] + the same offset, i = 0..n_peers-1 (peer-mapped device pointers of the other
+   * ranks' C buffers, already offset to this rank's row block). Plain stores, no multicast. */
+  int32_t n_peers;
+  int32_t reserved;
+  void* peer_c[8];
+} kcg_gemm_desc;
+
+/* O[B,H,Sq,D] = softmax(scale * Q.K^T [+ causal mask]) . V, tensors [B,H,S,D] contiguous
+ * (test/test.cc:71-90).  Replaces the kernel FMHAOptimizer builds from the
+ * BatchedMatmul -> Softmax -> BatchedMatmul chain (src/Optimizer/Optimizer.cc:1079-1333).
+ * scale = 1 and causal = 0 reproduce the reference's graph exactly
+ * (src/Frontend/Operators.cc:504-534 has neither scale nor mask). */
+typedef struct kcg_fmha_desc {
+  int32_t B, H;
+  int32_t Sq, Skv;
+  int32_t D;          /* head dim: 64 or 128 */
+  int32_t dtype_in;   /* kcg_dtype_t of Q, K, V (F32 inputs are rounded to bf16 in scratch) */
+  int32_t dtype_out;  /* kcg_dtype_t of O */
+  int32_t causal;     /* 0 / 1 : query i sees keys j <= i + (Skv - Sq) */
+  float scale;        /* multiplies the logits before exp */
+  int32_t reserved;
+} kcg_fmha_desc;
+
+/* Scratch the launch needs (bytes; may be 0). 3xTF32 GEMM: hi/lo split copies of A and B.
+ * FMHA with f32 inputs: bf16 copies of Q, K, V. */
+size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d);
+size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d);
+
+/* Replaces: launch of `<graph>::kernel0(A, B, C)` emitted by CUDAGen
+ * (src/Backend/CUDA.cc:773-857) for the scheduled Matmul func, with Relu fused. */
+kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces: launch of `Fused_Multi_Head_Attention_*::kernel0(Q, K, V, O)`
+ * (src/Optimizer/Optimizer.cc:1101-1111, src/Backend/CUDA.cc:773-857). */
+kcg_status_t kcg_fmha_fwd_launch(const kcg_fmha_desc* d, const void* Q, const void* K,
+                                 const void* V, void* O, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
+/* Host-buffer convenience forms (what the reference's absent harness did around the kernel:
+ * cudaMalloc, H2D, launch, D2H -- performance/output.log:6-13).  They allocate device
+ * buffers, copy, launch on `stream`, copy back and synchronise. */
+kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC);
+kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const void* hK,
+                               const void* hV, void* hO);
+
+/* Reads (and clears) the status word of the current device that a kernel sets when one of
+ * its bounded waits runs out; 0 = no timeout.  Synchronises the device. */
+int kcg_last_device_status(void);
+
+/* Test hook: iteration cap of the device-side waits for subsequent launches (0 = default). */
+void kcg_set_spin_limit(uint32_t iterations);
+
+/* Number of kernel launches this library has issued since load (all threads). */
+uint64_t kcg_launch_count(void);
+
+const char* kcg_status_str(kcg_status_t s);
+const char* kcg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KCG_CAPI_H_ */

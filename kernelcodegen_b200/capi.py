@@ -1,0 +1,122 @@
+"""ctypes binding of the C-ABI in `include/kcg_capi.h`.
+
+The library is loaded from the package directory (`libkcg_b200.so`, built in-tree by
+`kernelcodegen_b200.build`).  There is no fallback: if the library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libkcg_b200.so"
+
+# enum kcg_status_t
+KCG_OK = 0
+KCG_BAD_SHAPE = 1
+KCG_BAD_ALIGN = 2
+KCG_UNSUPPORTED = 3
+KCG_CUDA_ERROR = 4
+KCG_DEVICE_TIMEOUT = 5
+KCG_PEER_TIMEOUT = 6
+KCG_NCCL_ERROR = 7
+KCG_BAD_WORKSPACE = 8
+KCG_BAD_ARGUMENT = 9
+
+# enum kcg_dtype_t / kcg_precision_t / kcg_epilogue_t / kcg_layout_t
+KCG_F32, KCG_BF16 = 0, 1
+KCG_PREC_3XTF32, KCG_PREC_TF32, KCG_PREC_BF16 = 0, 1, 2
+KCG_EPI_NONE, KCG_EPI_RELU = 0, 1
+KCG_ROW_MAJOR, KCG_COL_MAJOR = 0, 1
+
+EXPORTED_SYMBOLS = (
+    "kcg_gemm_workspace_bytes",
+    "kcg_fmha_workspace_bytes",
+    "kcg_gemm_launch",
+    "kcg_fmha_fwd_launch",
+    "kcg_gemm_host",
+    "kcg_fmha_fwd_host",
+    "kcg_last_device_status",
+    "kcg_set_spin_limit",
+    "kcg_launch_count",
+    "kcg_status_str",
+    "kcg_version",
+)
+
+
+class GemmDesc(Structure):
+    """Mirror of `struct kcg_gemm_desc`."""
+
+    _fields_ = [
+        ("M", c_int64), ("N", c_int64), ("K", c_int64),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("dtype_in", c_int32), ("dtype_out", c_int32),
+        ("precision", c_int32), ("epilogue", c_int32), ("b_layout", c_int32),
+        ("tile_n", c_int32), ("stages", c_int32), ("group_m", c_int32),
+        ("n_peers", c_int32), ("reserved", c_int32),
+        ("peer_c", c_void_p * 8),
+    ]
+
+
+class FmhaDesc(Structure):
+    """Mirror of `struct kcg_fmha_desc`."""
+
+    _fields_ = [
+        ("B", c_int32), ("H", c_int32), ("Sq", c_int32), ("Skv", c_int32), ("D", c_int32),
+        ("dtype_in", c_int32), ("dtype_out", c_int32), ("causal", c_int32),
+        ("scale", c_float), ("reserved", c_int32),
+    ]
+
+
+class KcgError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: {status_str(status)}")
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the native library once; raise if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m kernelcodegen_b200.build` "
+            "(there is no CPU or PyTorch fallback)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.kcg_gemm_workspace_bytes.restype = c_size_t
+    lib.kcg_gemm_workspace_bytes.argtypes = [POINTER(GemmDesc)]
+    lib.kcg_fmha_workspace_bytes.restype = c_size_t
+    lib.kcg_fmha_workspace_bytes.argtypes = [POINTER(FmhaDesc)]
+    lib.kcg_gemm_launch.restype = c_int
+    lib.kcg_gemm_launch.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.kcg_fmha_fwd_launch.restype = c_int
+    lib.kcg_fmha_fwd_launch.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.kcg_gemm_host.restype = c_int
+    lib.kcg_gemm_host.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p]
+    lib.kcg_fmha_fwd_host.restype = c_int
+    lib.kcg_fmha_fwd_host.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.kcg_last_device_status.restype = c_int
+    lib.kcg_last_device_status.argtypes = []
+    lib.kcg_set_spin_limit.restype = None
+    lib.kcg_set_spin_limit.argtypes = [c_uint32]
+    lib.kcg_launch_count.restype = c_uint64
+    lib.kcg_launch_count.argtypes = []
+    lib.kcg_status_str.restype = c_char_p
+    lib.kcg_status_str.argtypes = [c_int]
+    lib.kcg_version.restype = c_char_p
+    lib.kcg_version.argtypes = []
+    _lib = lib
+    return lib
+
+
+def status_str(status: int) -> str:
+    return load().kcg_status_str(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != KCG_OK:
+        raise KcgError(status, what)

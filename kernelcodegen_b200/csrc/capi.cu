@@ -1,0 +1,209 @@
+// extern "C" surface of the library (declared in include/kcg_capi.h) plus the host-side
+// plumbing the launchers share.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace kcg {
+
+std::atomic<uint64_t> g_launches{0};
+std::atomic<uint32_t> g_spin_limit{0};
+
+// One status word per device (a __device__ variable is instantiated on every device that
+// loads the module).  Kernels receive its address as a parameter.
+__device__ int g_device_status;
+
+kcg_status_t device_status_ptr(int** out) {
+  static std::mutex mu;
+  static int* cache[64] = {};
+  int dev = 0;
+  KCG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KCG_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    KCG_CUDA_TRY(cudaGetSymbolAddress(&p, g_device_status));
+    KCG_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
+    cache[dev] = static_cast<int*>(p);
+  }
+  *out = cache[dev];
+  return KCG_OK;
+}
+
+int device_sm_count() {
+  static int cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (!cache[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 1;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+kcg_status_t encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
+                         const uint64_t* dims, const uint64_t* strides_bytes,
+                         const uint32_t* box, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    std::fprintf(stderr, "kcg: cuTensorMapEncodeTiled not available (no CUDA driver?)\n");
+    return KCG_CUDA_ERROR;
+  }
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
+  CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides,
+                  gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr, "kcg: cuTensorMapEncodeTiled failed with CUresult %d\n",
+                 static_cast<int>(r));
+    return KCG_CUDA_ERROR;
+  }
+  return KCG_OK;
+}
+
+// Host-buffer helper: device buffer that frees itself.
+struct DevBuf {
+  void* p = nullptr;
+  ~DevBuf() {
+    if (p) cudaFree(p);
+  }
+  cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 1); }
+};
+
+}  // namespace kcg
+
+using namespace kcg;
+
+extern "C" {
+
+size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d) { return gemm_workspace_impl(d); }
+size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d) { return fmha_workspace_impl(d); }
+
+kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_launch_impl(d, A, B, C, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream));
+}
+
+kcg_status_t kcg_fmha_fwd_launch(const kcg_fmha_desc* d, const void* Q, const void* K,
+                                 const void* V, void* O, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  return fmha_launch_impl(d, Q, K, V, O, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream));
+}
+
+kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC) {
+  if (!d || !hA || !hB || !hC) return KCG_BAD_ARGUMENT;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
+  if (d->n_peers != 0) return KCG_UNSUPPORTED;
+  const size_t es = d->dtype_in == KCG_BF16 ? 2 : 4;
+  const size_t os = d->dtype_out == KCG_BF16 ? 2 : 4;
+  const bool bk = d->b_layout == KCG_COL_MAJOR;
+  if (d->lda < d->K || d->ldc < d->N || d->ldb < (bk ? d->K : d->N)) return KCG_BAD_SHAPE;
+  const size_t a_bytes = static_cast<size_t>(d->M) * d->lda * es;
+  const size_t b_bytes = static_cast<size_t>(bk ? d->N : d->K) * d->ldb * es;
+  const size_t c_bytes = static_cast<size_t>(d->M) * d->ldc * os;
+  const size_t ws_bytes = gemm_workspace_impl(d);
+  DevBuf a, b, c, ws;
+  KCG_CUDA_TRY(a.alloc(a_bytes));
+  KCG_CUDA_TRY(b.alloc(b_bytes));
+  KCG_CUDA_TRY(c.alloc(c_bytes));
+  KCG_CUDA_TRY(ws.alloc(ws_bytes));
+  KCG_CUDA_TRY(cudaMemcpy(a.p, hA, a_bytes, cudaMemcpyHostToDevice));
+  KCG_CUDA_TRY(cudaMemcpy(b.p, hB, b_bytes, cudaMemcpyHostToDevice));
+  if (d->ldc != d->N) KCG_CUDA_TRY(cudaMemcpy(c.p, hC, c_bytes, cudaMemcpyHostToDevice));
+  kcg_status_t st = gemm_launch_impl(d, a.p, b.p, c.p, ws.p, ws_bytes, nullptr);
+  if (st != KCG_OK) return st;
+  KCG_CUDA_TRY(cudaMemcpy(hC, c.p, c_bytes, cudaMemcpyDeviceToHost));
+  return kcg_last_device_status() ? KCG_DEVICE_TIMEOUT : KCG_OK;
+}
+
+kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const void* hK,
+                               const void* hV, void* hO) {
+  if (!d || !hQ || !hK || !hV || !hO) return KCG_BAD_ARGUMENT;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0 || d->D <= 0) return KCG_BAD_SHAPE;
+  const size_t es = d->dtype_in == KCG_BF16 ? 2 : 4;
+  const size_t os = d->dtype_out == KCG_BF16 ? 2 : 4;
+  const size_t bh = static_cast<size_t>(d->B) * d->H;
+  const size_t q_bytes = bh * d->Sq * d->D * es;
+  const size_t kv_bytes = bh * d->Skv * d->D * es;
+  const size_t o_bytes = bh * d->Sq * d->D * os;
+  const size_t ws_bytes = fmha_workspace_impl(d);
+  DevBuf q, k, v, o, ws;
+  KCG_CUDA_TRY(q.alloc(q_bytes));
+  KCG_CUDA_TRY(k.alloc(kv_bytes));
+  KCG_CUDA_TRY(v.alloc(kv_bytes));
+  KCG_CUDA_TRY(o.alloc(o_bytes));
+  KCG_CUDA_TRY(ws.alloc(ws_bytes));
+  KCG_CUDA_TRY(cudaMemcpy(q.p, hQ, q_bytes, cudaMemcpyHostToDevice));
+  KCG_CUDA_TRY(cudaMemcpy(k.p, hK, kv_bytes, cudaMemcpyHostToDevice));
+  KCG_CUDA_TRY(cudaMemcpy(v.p, hV, kv_bytes, cudaMemcpyHostToDevice));
+  kcg_status_t st = fmha_launch_impl(d, q.p, k.p, v.p, o.p, ws.p, ws_bytes, nullptr);
+  if (st != KCG_OK) return st;
+  KCG_CUDA_TRY(cudaMemcpy(hO, o.p, o_bytes, cudaMemcpyDeviceToHost));
+  return kcg_last_device_status() ? KCG_DEVICE_TIMEOUT : KCG_OK;
+}
+
+int kcg_last_device_status(void) {
+  int* p = nullptr;
+  if (device_status_ptr(&p) != KCG_OK) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) cudaMemset(p, 0, sizeof(int));
+  return v;
+}
+
+void kcg_set_spin_limit(uint32_t iterations) { g_spin_limit.store(iterations); }
+
+uint64_t kcg_launch_count(void) { return g_launches.load(); }
+
+const char* kcg_status_str(kcg_status_t s) {
+  switch (s) {
+    case KCG_OK: return "KCG_OK";
+    case KCG_BAD_SHAPE: return "KCG_BAD_SHAPE";
+    case KCG_BAD_ALIGN: return "KCG_BAD_ALIGN";
+    case KCG_UNSUPPORTED: return "KCG_UNSUPPORTED";
+    case KCG_CUDA_ERROR: return "KCG_CUDA_ERROR";
+    case KCG_DEVICE_TIMEOUT: return "KCG_DEVICE_TIMEOUT";
+    case KCG_PEER_TIMEOUT: return "KCG_PEER_TIMEOUT";
+    case KCG_NCCL_ERROR: return "KCG_NCCL_ERROR";
+    case KCG_BAD_WORKSPACE: return "KCG_BAD_WORKSPACE";
+    case KCG_BAD_ARGUMENT: return "KCG_BAD_ARGUMENT";
+  }
+  return "KCG_UNKNOWN";
+}
+
+const char* kcg_version(void) { return "kcg-b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

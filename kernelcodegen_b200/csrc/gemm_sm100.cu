@@ -1,0 +1,519 @@
+// C[M,N] = epilogue(A[M,K] . B) on the 5th-generation tensor cores of sm_100a.
+//
+// The computation is the loop nest Matmul::build emits in the reference
+// (src/Frontend/Operators.cc:140-173: C[i,j] = sum_k A[i,k]*B[k,j], fp32) followed by the
+// elementwise max(0, x) of Relu::build (src/Frontend/Operators.cc:232-244), fused into the
+// epilogue.  The reference schedules that nest for CUDA cores (128x128x8 CTA tile, 8x8 thread
+// tile, src/Optimizer/Optimizer.cc:383-548); here the same roles are played by hardware units:
+//
+//   warp 0      TMA producer : global -> 128B-swizzled shared memory, STAGES-deep mbarrier ring
+//   warp 1      UMMA issuer  : tcgen05.mma 128 x BN x (32 bytes of K), accumulators in TMEM,
+//                              two accumulator buffers so tile i+1 starts while tile i drains
+//   warps 2..5  epilogue     : tcgen05.ld -> ReLU -> (bf16 pack) -> global stores
+//                              (and, for the fused all-gather, the same stores to peer GPUs)
+//
+// The grid is persistent (one CTA per SM); tiles are walked in groups of `group_m` row blocks
+// so that concurrently running CTAs share A and B panels in L2.
+//
+// Precisions (KIND): 0 = bf16 inputs, 1 = single TF32 product of fp32 inputs,
+// 2 = 3xTF32: four operand tiles per stage (A_hi, A_lo, B_hi, B_lo) and three UMMA passes
+//     a_lo*b_hi + a_hi*b_lo + a_hi*b_hi accumulated in fp32.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace kcg {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in limit per CTA
+
+struct GemmParams {
+  void* C;
+  int M, N, K;
+  long long ldc;
+  int tiles_m, tiles_n, group_m;
+  int relu;
+  int* status;
+  uint32_t spin;
+  int n_peers;
+  void* peers[8];
+};
+
+template <int KIND, int BN>
+struct GemmCfg {
+  static constexpr int ES = (KIND == 0) ? 2 : 4;     // bytes per input element
+  static constexpr int BK = 128 / ES;                // one 128-byte swizzle row of K
+  static constexpr int UK = 32 / ES;                 // K per UMMA instruction
+  static constexpr int NOPS = (KIND == 2) ? 2 : 1;   // hi/lo copies per operand
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = NOPS * (A_BYTES + B_BYTES);
+  static constexpr int CTRL_BYTES = 1024;            // barriers, TMEM pointer, abort flag
+  static constexpr int MAX_STAGES = (SMEM_LIMIT - CTRL_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;           // two accumulator buffers (256 or 512)
+};
+
+template <int KIND, int BN, int STAGES, bool B_KMAJOR, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+            const GemmParams p) {
+  using Cfg = GemmCfg<KIND, BN>;
+  constexpr int ES = Cfg::ES, BK = Cfg::BK, UK = Cfg::UK;
+  constexpr int A_BYTES = Cfg::A_BYTES, B_BYTES = Cfg::B_BYTES;
+  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+  constexpr uint32_t FMT = (KIND == 0) ? UMMA_FMT_BF16 : UMMA_FMT_TF32;
+  constexpr uint32_t IDESC = make_idesc(FMT, BM, BN, 0, B_KMAJOR ? 0 : 1);
+  // B in [K,N] row-major form is "MN-major": shared memory holds BN/(BK) column groups, each
+  // BK k-rows of 128 bytes; successive groups are B_GROUP bytes apart.
+  constexpr int B_NGROUP = 128 / ES;                 // n-elements per 128-byte row
+  constexpr int B_GROUP = BK * 128;                  // bytes of one [BK x 128B] group
+  constexpr uint32_t B_LBO = B_KMAJOR ? 16 : B_GROUP;
+  constexpr uint32_t B_KSTEP = B_KMAJOR ? 32 : UK * 128;
+  // fp32 operands stored along N use the 32-byte-atom swizzle (4-row period).
+  constexpr bool B_ATOM32 = (!B_KMAJOR) && ES == 4;
+  constexpr uint32_t B_SBO = B_ATOM32 ? 512 : 1024;
+  constexpr uint32_t B_LAYOUT = B_ATOM32 ? SMEM_LAYOUT_SW128_ATOM32 : SMEM_LAYOUT_SW128;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;      // swizzle atoms need 1024-byte alignment
+  uint8_t* ctrl = smem_raw + (base - raw) + STAGES * STAGE_BYTES;
+  const uint32_t ctrl_u = base + STAGES * STAGE_BYTES;
+  // control block: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2] | tmem ptr | abort
+  const uint32_t bar_full = ctrl_u;
+  const uint32_t bar_empty = ctrl_u + 8 * STAGES;
+  const uint32_t bar_tfull = ctrl_u + 16 * STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(ctrl + 16 * STAGES + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * STAGES + 36);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (KIND == 2) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_per_group = p.group_m * p.tiles_n;
+
+  auto tile_coord = [&](int t, int& mb, int& nb) {
+    const int g = t / tiles_per_group;
+    const int first_m = g * p.group_m;
+    const int gm = min(p.group_m, p.tiles_m - first_m);
+    const int r = t - g * tiles_per_group;
+    mb = first_m + r % gm;
+    nb = r / gm;
+  };
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coord(t, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status,
+                         DEV_TIMEOUT_PRODUCER, p.spin);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t sA = base + stage * STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::NOPS * A_BYTES;
+          mbar_expect_tx(full, STAGE_BYTES);
+          const int k0 = kb * BK;
+          tma_load_2d(sA, &tmA, full, k0, m0);
+          if (KIND == 2) tma_load_2d(sA + A_BYTES, &tmA2, full, k0, m0);
+          if (B_KMAJOR) {
+            tma_load_2d(sB, &tmB, full, k0, n0);
+            if (KIND == 2) tma_load_2d(sB + B_BYTES, &tmB2, full, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / B_NGROUP; ++j) {
+              tma_load_2d(sB + j * B_GROUP, &tmB, full, n0 + j * B_NGROUP, k0);
+              if (KIND == 2)
+                tma_load_2d(sB + B_BYTES + j * B_GROUP, &tmB2, full, n0 + j * B_NGROUP, k0);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Unwinding: let copies already in flight land before the CTA's shared memory goes
+        // away.  Stages before `stage` were armed in the current phase, the others in the
+        // previous one (a never-armed barrier passes a wait on parity 1 at once).
+        for (int s = 0; s < STAGES; ++s) {
+          const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+          for (uint32_t it = 0; it < 4096u; ++it)
+            if (mbar_try_wait(bar_full + 8 * s, par)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer ---------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status,
+                       DEV_TIMEOUT_MMA_TMEM, p.spin);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL,
+                         p.spin);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sA = base + stage * STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::NOPS * A_BYTES;
+          if (KIND == 2) {
+            // small terms first: a_lo*b_hi, a_hi*b_lo, then a_hi*b_hi
+#pragma unroll
+            for (int pass = 0; pass < 3; ++pass) {
+              const uint32_t a_off = (pass == 0) ? A_BYTES : 0;
+              const uint32_t b_off = (pass == 1) ? B_BYTES : 0;
+#pragma unroll
+              for (int k = 0; k < BK / UK; ++k) {
+                const uint64_t ad = make_smem_desc(sA + a_off + k * 32, 16, 1024);
+                const uint64_t bd = make_smem_desc(sB + b_off + k * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+                umma_tf32_ss(d_tmem, ad, bd, IDESC, (kb | pass | k) ? 1u : 0u);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / UK; ++k) {
+              const uint64_t ad = make_smem_desc(sA + k * 32, 16, 1024);
+              const uint64_t bd = make_smem_desc(sB + k * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+              if (KIND == 0)
+                umma_bf16_ss(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
+              else
+                umma_tf32_ss(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
+            }
+          }
+          umma_commit(bar_empty + 8 * stage);  // stage reusable once these UMMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (4 warps) --------------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int local = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      int mb, nb;
+      tile_coord(t, mb, nb);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE,
+                     p.spin);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = mb * BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = nb * BN + c0;
+        if (col >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = (r[i] & 0x80000000u) ? 0u : r[i];
+        }
+        if (row < p.M) {
+          const long long off = static_cast<long long>(row) * p.ldc + col;
+          if (sizeof(OutT) == 2) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            for (int dst = 0; dst <= p.n_peers; ++dst) {
+              OutT* cp = static_cast<OutT*>(dst == 0 ? p.C : p.peers[dst - 1]) + off;
+              if (col + 32 <= p.N) {
+                uint4* v = reinterpret_cast<uint4*>(cp);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  v[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+              } else {
+                unsigned short* s = reinterpret_cast<unsigned short*>(cp);
+                for (int i = 0; i < 32 && col + i < p.N; ++i)
+                  s[i] = static_cast<unsigned short>((i & 1) ? (pk[i >> 1] >> 16)
+                                                             : (pk[i >> 1] & 0xFFFFu));
+              }
+            }
+          } else {
+            for (int dst = 0; dst <= p.n_peers; ++dst) {
+              OutT* cp = static_cast<OutT*>(dst == 0 ? p.C : p.peers[dst - 1]) + off;
+              if (col + 32 <= p.N) {
+                uint4* v = reinterpret_cast<uint4*>(cp);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  v[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+              } else {
+                uint32_t* s = reinterpret_cast<uint32_t*>(cp);
+                for (int i = 0; i < 32 && col + i < p.N; ++i) s[i] = r[i];
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + 8 * acc);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// fp32 -> (hi, lo) with hi = x with the 13 low mantissa bits cleared (exactly representable in
+// TF32, so the tensor core sees it unchanged whatever its input rounding) and lo = x - hi
+// (exact in fp32).  Output is compact [rows, cols].
+__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi,
+                                  float* __restrict__ lo, long long rows, int cols4,
+                                  long long ld) {
+  const long long total = rows * cols4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols4;
+    const int c = static_cast<int>(i - r * cols4);
+    const float4 v = *reinterpret_cast<const float4*>(src + r * ld + 4ll * c);
+    float4 h, l;
+    h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+    h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+    h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+    h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+    l.x = v.x - h.x;
+    l.y = v.y - h.y;
+    l.z = v.z - h.z;
+    l.w = v.w - h.w;
+    reinterpret_cast<float4*>(hi)[i] = h;
+    reinterpret_cast<float4*>(lo)[i] = l;
+  }
+}
+
+inline size_t pad256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+template <int KIND, int BN, bool B_KMAJOR, typename OutT>
+kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
+                             const CUtensorMap& tB2, const GemmParams& p, int stages_req,
+                             cudaStream_t stream) {
+  using Cfg = GemmCfg<KIND, BN>;
+  constexpr int STAGES = Cfg::MAX_STAGES > 8 ? 8 : Cfg::MAX_STAGES;
+  static_assert(STAGES >= 2, "need at least two pipeline stages");
+  if (stages_req != 0 && stages_req != STAGES) return KCG_UNSUPPORTED;
+  auto kern = gemm_kernel<KIND, BN, STAGES, B_KMAJOR, OutT>;
+  constexpr int smem = STAGES * Cfg::STAGE_BYTES + Cfg::CTRL_BYTES + 1024;
+  static_assert(smem <= SMEM_LIMIT, "shared memory budget");
+  KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int sms = device_sm_count();
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(tA, tB, tA2, tB2, p);
+  g_launches.fetch_add(1);
+  KCG_CUDA_TRY(cudaGetLastError());
+  return KCG_OK;
+}
+
+template <int KIND, typename OutT>
+kcg_status_t dispatch_shape(int bn, bool b_kmajor, const CUtensorMap& tA, const CUtensorMap& tB,
+                            const CUtensorMap& tA2, const CUtensorMap& tB2, const GemmParams& p,
+                            int stages, cudaStream_t s) {
+  if (bn == 256) {
+    return b_kmajor ? launch_instance<KIND, 256, true, OutT>(tA, tB, tA2, tB2, p, stages, s)
+                    : launch_instance<KIND, 256, false, OutT>(tA, tB, tA2, tB2, p, stages, s);
+  }
+  if (bn == 128) {
+    return b_kmajor ? launch_instance<KIND, 128, true, OutT>(tA, tB, tA2, tB2, p, stages, s)
+                    : launch_instance<KIND, 128, false, OutT>(tA, tB, tA2, tB2, p, stages, s);
+  }
+  return KCG_UNSUPPORTED;
+}
+
+}  // namespace
+
+size_t gemm_workspace_impl(const kcg_gemm_desc* d) {
+  if (!d || d->precision != KCG_PREC_3XTF32) return 0;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
+  const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
+  const size_t b = pad256(static_cast<size_t>(d->K) * d->N * 4);
+  return 2 * a + 2 * b;
+}
+
+kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                              void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (!d || !A || !B || !C) return KCG_BAD_ARGUMENT;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
+  if (d->M > 0x7FFFFFFF || d->N > 0x7FFFFFFF || d->K > 0x7FFFFFFF) return KCG_BAD_SHAPE;
+  const bool b_kmajor = d->b_layout == KCG_COL_MAJOR;
+  if (d->b_layout != KCG_ROW_MAJOR && d->b_layout != KCG_COL_MAJOR) return KCG_UNSUPPORTED;
+  if (d->lda < d->K || d->ldc < d->N || d->ldb < (b_kmajor ? d->K : d->N)) return KCG_BAD_SHAPE;
+  int kind;
+  if (d->precision == KCG_PREC_BF16) {
+    if (d->dtype_in != KCG_BF16) return KCG_UNSUPPORTED;
+    if (d->dtype_out != KCG_BF16 && d->dtype_out != KCG_F32) return KCG_UNSUPPORTED;
+    kind = 0;
+  } else if (d->precision == KCG_PREC_TF32 || d->precision == KCG_PREC_3XTF32) {
+    if (d->dtype_in != KCG_F32 || d->dtype_out != KCG_F32) return KCG_UNSUPPORTED;
+    kind = d->precision == KCG_PREC_TF32 ? 1 : 2;
+  } else {
+    return KCG_UNSUPPORTED;
+  }
+  if (d->epilogue != KCG_EPI_NONE && d->epilogue != KCG_EPI_RELU) return KCG_UNSUPPORTED;
+  if (d->n_peers < 0 || d->n_peers > 8) return KCG_BAD_ARGUMENT;
+  const int es = kind == 0 ? 2 : 4;
+  const int os = d->dtype_out == KCG_BF16 ? 2 : 4;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return KCG_BAD_ALIGN;
+  if ((d->lda * es) % 16 || (d->ldb * es) % 16 || (d->ldc * os) % 16) return KCG_BAD_ALIGN;
+  for (int i = 0; i < d->n_peers; ++i)
+    if (!d->peer_c[i] || !aligned16(d->peer_c[i])) return KCG_BAD_ALIGN;
+  int bn = d->tile_n;
+  if (bn == 0) bn = (kind == 2) ? 128 : 256;
+  if (bn != 128 && bn != 256) return KCG_UNSUPPORTED;
+
+  const void* pa = A;
+  const void* pb = B;
+  const void* pa2 = A;
+  const void* pb2 = B;
+  long long lda = d->lda, ldb = d->ldb;
+  if (kind == 2) {
+    const size_t need = gemm_workspace_impl(d);
+    if (!ws || ws_bytes < need || !aligned16(ws)) return KCG_BAD_WORKSPACE;
+    if ((d->K % 4) || (d->N % 4)) return KCG_BAD_ALIGN;
+    const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
+    const size_t b = pad256(static_cast<size_t>(d->K) * d->N * 4);
+    float* a_hi = static_cast<float*>(ws);
+    float* a_lo = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + a);
+    float* b_hi = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + 2 * a);
+    float* b_lo = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + 2 * a + b);
+    const int sms = device_sm_count();
+    const long long b_rows = b_kmajor ? d->N : d->K;
+    const long long b_cols = b_kmajor ? d->K : d->N;
+    split_tf32_kernel<<<sms * 4, 256, 0, stream>>>(static_cast<const float*>(A), a_hi, a_lo, d->M,
+                                                    static_cast<int>(d->K / 4), d->lda);
+    split_tf32_kernel<<<sms * 4, 256, 0, stream>>>(static_cast<const float*>(B), b_hi, b_lo,
+                                                    b_rows, static_cast<int>(b_cols / 4), d->ldb);
+    g_launches.fetch_add(2);
+    KCG_CUDA_TRY(cudaGetLastError());
+    pa = a_hi;
+    pa2 = a_lo;
+    pb = b_hi;
+    pb2 = b_lo;
+    lda = d->K;
+    ldb = b_cols;
+  }
+
+  using Cfg0 = GemmCfg<0, 128>;
+  (void)sizeof(Cfg0);
+  const CUtensorMapDataType dt =
+      kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const uint32_t bk = 128 / es;
+  CUtensorMap tA, tB, tA2, tB2;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * es};
+    const uint32_t box[2] = {bk, BM};
+    kcg_status_t st = encode_tmap(&tA, dt, 2, pa, dims, strides, box);
+    if (st != KCG_OK) return st;
+    st = encode_tmap(&tA2, dt, 2, pa2, dims, strides, box);
+    if (st != KCG_OK) return st;
+  }
+  {
+    uint64_t dims[2];
+    uint32_t box[2];
+    if (b_kmajor) {  // B stored [N, K]
+      dims[0] = d->K;
+      dims[1] = d->N;
+      box[0] = bk;
+      box[1] = bn;
+    } else {  // B stored [K, N]
+      dims[0] = d->N;
+      dims[1] = d->K;
+      box[0] = 128 / es;
+      box[1] = bk;
+    }
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * es};
+    const CUtensorMapSwizzle sw = (!b_kmajor && es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                         : CU_TENSOR_MAP_SWIZZLE_128B;
+    kcg_status_t st = encode_tmap(&tB, dt, 2, pb, dims, strides, box, sw);
+    if (st != KCG_OK) return st;
+    st = encode_tmap(&tB2, dt, 2, pb2, dims, strides, box, sw);
+    if (st != KCG_OK) return st;
+  }
+
+  GemmParams p;
+  p.C = C;
+  p.M = static_cast<int>(d->M);
+  p.N = static_cast<int>(d->N);
+  p.K = static_cast<int>(d->K);
+  p.ldc = d->ldc;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + bn - 1) / bn;
+  p.group_m = d->group_m > 0 ? d->group_m : 16;
+  p.relu = d->epilogue == KCG_EPI_RELU;
+  kcg_status_t st = device_status_ptr(&p.status);
+  if (st != KCG_OK) return st;
+  const uint32_t spin = g_spin_limit.load();
+  p.spin = spin ? spin : KCG_SPIN_LIMIT;
+  p.n_peers = d->n_peers;
+  for (int i = 0; i < 8; ++i) p.peers[i] = i < d->n_peers ? d->peer_c[i] : nullptr;
+
+  if (kind == 0) {
+    if (d->dtype_out == KCG_BF16)
+      return dispatch_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages,
+                                              stream);
+    return dispatch_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+  }
+  if (kind == 1) return dispatch_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+  return dispatch_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+}
+
+}  // namespace kcg
