@@ -1,5 +1,465 @@
+// O = softmax(scale * Q.K^T [causal]) . V on sm_100a, one CTA per (batch*head, 128-query tile).
+//
+// The computation is the reference's three-operator graph (test/test.cc:88-90):
+// BatchedMatmul(Q, K colMajor) (src/Frontend/Operators.cc:353-414), Softmax over the last axis
+// (:474-536) and BatchedMatmul(P, V).  The reference's FMHAOptimizer fuses that chain into a
+// FlashAttention-2 style kernel with scalar FFMA outer products and shuffle reductions
+// (src/Optimizer/Optimizer.cc:1079-1333); here both contractions run on tcgen05 tensor cores
+// and the online softmax works on rows read straight out of TMEM:
+//
+//   warp 0      TMA producer : Q once, then K_j / V_j blocks (128 keys) through 2-stage rings
+//   warp 1      UMMA issuer  : S_j = Q.K_j^T -> TMEM (two S buffers), O_j = P_j.V_j -> TMEM
+//   warps 2..5  softmax      : thread t owns query row t: tcgen05.ld its S row, running max /
+//                              sum (thread-local: one row never spans lanes in this TMEM
+//                              layout), P_j = exp2(...) as bf16 into swizzled shared memory,
+//                              O += rescaled P_j.V_j in registers, final O / l -> global
+//
+// Online softmax: m_j = max(m_{j-1}, rowmax(S_j)), alpha_j = exp(scale*(m_{j-1}-m_j)),
+// l_j = alpha_j*l_{j-1} + rowsum(P_j), O_j = alpha_j*O_{j-1} + P_j.V_j, out = O_n / l_n --
+// mathematically the reference's exp(x)/sum(exp(x)) (no max subtraction there), evaluated
+// without overflow.
 #include "common.cuh"
+#include "ptx.cuh"
+
 namespace kcg {
-size_t fmha_workspace_impl(const kcg_fmha_desc*) { return 0; }
-kcg_status_t fmha_launch_impl(const kcg_fmha_desc*, const void*, const void*, const void*, void*, void*, size_t, cudaStream_t) { return KCG_UNSUPPORTED; }
+
+namespace {
+
+constexpr int FM_THREADS = 192;
+constexpr int BQ = 128;   // query rows per CTA
+constexpr int BKV = 128;  // keys per block
+
+struct FmhaParams {
+  void* O;
+  int Sq, Skv;
+  int causal;
+  int out_bf16;
+  float scale_log2;  // scale * log2(e)
+  int* status;
+  uint32_t spin;
+};
+
+template <int D>
+struct FmhaCfg {
+  static constexpr int TILE_BYTES = 128 * D * 2;      // Q, K_j, V_j tile: 128 rows x D bf16
+  static constexpr int PANEL_BYTES = 128 * 128;       // 128 rows x 64 bf16 (one swizzle panel)
+  static constexpr int P_BYTES = BQ * BKV * 2;        // 32 KB
+  static constexpr int SMEM_DATA = TILE_BYTES /*Q*/ + 2 * TILE_BYTES /*K*/ + 2 * TILE_BYTES /*V*/ + P_BYTES;
+  static constexpr int SMEM_TOTAL = SMEM_DATA + 1024 /*ctrl*/ + 1024 /*align slack*/;
+  static constexpr int TMEM_COLS = 512;               // S0 | S1 | PV
+};
+
+template <int D>
+__global__ void __launch_bounds__(FM_THREADS, 1)
+fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const FmhaParams p) {
+  using Cfg = FmhaCfg<D>;
+  constexpr int TILE = Cfg::TILE_BYTES;
+  constexpr int PANEL = Cfg::PANEL_BYTES;
+  constexpr int DPANELS = D / 64;
+  constexpr uint32_t IDESC_S = make_idesc(UMMA_FMT_BF16, BQ, BKV, 0, 0);
+  constexpr uint32_t IDESC_PV = make_idesc(UMMA_FMT_BF16, BQ, D, 0, 1);
+  constexpr uint32_t TM_S = 0, TM_PV = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t sQ = base;
+  const uint32_t sK = sQ + TILE;
+  const uint32_t sV = sK + 2 * TILE;
+  const uint32_t sP = sV + 2 * TILE;
+  uint8_t* gP = gen_base + 5 * TILE;
+  const uint32_t ctrl_u = sP + Cfg::P_BYTES;
+  uint8_t* ctrl = gen_base + Cfg::SMEM_DATA;
+  const uint32_t bar_q = ctrl_u;
+  const uint32_t bar_kfull = ctrl_u + 8;     // [2]
+  const uint32_t bar_kempty = ctrl_u + 24;   // [2]
+  const uint32_t bar_vfull = ctrl_u + 40;    // [2]
+  const uint32_t bar_vempty = ctrl_u + 56;   // [2]
+  const uint32_t bar_sfull = ctrl_u + 72;    // [2]
+  const uint32_t bar_sempty = ctrl_u + 88;   // [2]
+  const uint32_t bar_pfull = ctrl_u + 104;
+  const uint32_t bar_pvfull = ctrl_u + 112;
+  const uint32_t bar_pvempty = ctrl_u + 120;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(ctrl + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 132);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  // heavy (late) query tiles first when causal
+  const int qt = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int q0 = qt * BQ;
+  const int shift = p.Skv - p.Sq;  // causal: query i sees keys j <= i + shift
+  int kv_end = p.Skv;
+  if (p.causal) {
+    const int lim = q0 + BQ + shift;  // exclusive bound for the last row of the tile
+    kv_end = lim < kv_end ? lim : kv_end;
+    if (kv_end < 0) kv_end = 0;
+  }
+  const int n_kv = (kv_end + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_kfull + 8 * i, 1);
+      mbar_init(bar_kempty + 8 * i, 1);
+      mbar_init(bar_vfull + 8 * i, 1);
+      mbar_init(bar_vempty + 8 * i, 1);
+      mbar_init(bar_sfull + 8 * i, 1);
+      mbar_init(bar_sempty + 8 * i, 128);
+    }
+    mbar_init(bar_pfull, 128);
+    mbar_init(bar_pvfull, 1);
+    mbar_init(bar_pvempty, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(bar_q, TILE);
+#pragma unroll
+      for (int dp = 0; dp < DPANELS; ++dp) tma_load_3d(sQ + dp * PANEL, &tmQ, bar_q, dp * 64, q0, bh);
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t par = ((j >> 1) & 1u) ^ 1u;
+        ok = mbar_wait(bar_kempty + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_PRODUCER, p.spin);
+        if (!ok) break;
+        mbar_expect_tx(bar_kfull + 8 * b, TILE);
+#pragma unroll
+        for (int dp = 0; dp < DPANELS; ++dp)
+          tma_load_3d(sK + b * TILE + dp * PANEL, &tmK, bar_kfull + 8 * b, dp * 64, j * BKV, bh);
+        ok = mbar_wait(bar_vempty + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_PRODUCER, p.spin);
+        if (!ok) break;
+        mbar_expect_tx(bar_vfull + 8 * b, TILE);
+#pragma unroll
+        for (int dp = 0; dp < DPANELS; ++dp)
+          tma_load_3d(sV + b * TILE + dp * PANEL, &tmV, bar_vfull + 8 * b, dp * 64, j * BKV, bh);
+      }
+      if (!ok) {
+        // give copies already in flight time to land before shared memory is released
+        for (uint32_t it = 0; it < 4096u; ++it) {
+          if (mbar_try_wait(bar_q, 0)) break;
+        }
+        for (int b = 0; b < 2; ++b)
+          for (uint32_t it = 0; it < 4096u; ++it) {
+            if (mbar_try_wait(bar_kfull + 8 * b, 0) | mbar_try_wait(bar_vfull + 8 * b, 0)) break;
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer ---------------------------------------------
+    if (lane == 0 && n_kv > 0) {
+      bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, DEV_TIMEOUT_Q, p.spin);
+      auto issue_s = [&](int j) -> bool {
+        const int b = j & 1;
+        const uint32_t par = (j >> 1) & 1u;
+        if (!mbar_wait(bar_kfull + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin))
+          return false;
+        if (!mbar_wait(bar_sempty + 8 * b, par ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM,
+                       p.spin))
+          return false;
+        tc_fence_after();
+        const uint32_t kb = sK + b * TILE;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
+          umma_bf16_ss(tmem_base + TM_S + b * BKV, make_smem_desc(sQ + off, 16, 1024),
+                       make_smem_desc(kb + off, 16, 1024), IDESC_S, ks ? 1u : 0u);
+        }
+        umma_commit(bar_kempty + 8 * b);
+        umma_commit(bar_sfull + 8 * b);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          ok = issue_s(j + 1);
+          if (!ok) break;
+        }
+        const int b = j & 1;
+        ok = mbar_wait(bar_vfull + 8 * b, (j >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL,
+                       p.spin) &&
+             mbar_wait(bar_pvempty, (j & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM,
+                       p.spin) &&
+             mbar_wait(bar_pfull, j & 1u, abort_flag, p.status, DEV_TIMEOUT_P, p.spin);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t vb = sV + b * TILE;
+#pragma unroll
+        for (int ks = 0; ks < BKV / 16; ++ks) {
+          const uint64_t pd = make_smem_desc(sP + (ks >> 2) * PANEL + (ks & 3) * 32, 16, 1024);
+          // V tile: D/64 groups of [128 keys x 128 bytes]; 16 keys = 2048 bytes
+          const uint64_t vd = make_smem_desc(vb + ks * 2048, PANEL, 1024);
+          umma_bf16_ss(tmem_base + TM_PV, pd, vd, IDESC_PV, ks ? 1u : 0u);
+        }
+        umma_commit(bar_vempty + 8 * b);
+        umma_commit(bar_pvfull);
+      }
+    }
+  } else {
+    // ------------------------------- softmax / output (4 warps) ------------------------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;          // row inside the tile == TMEM lane
+    const int row = q0 + r;               // query index
+    const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
+    const float c = p.scale_log2;
+    int limit = p.Skv;                    // keys [0, limit) are visible to this row
+    if (p.causal) {
+      const int l2 = row + shift + 1;
+      limit = l2 < limit ? l2 : limit;
+    }
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(bar_sfull + 8 * b, (j >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_SOFTMAX,
+                     p.spin);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_s = tmem_base + TM_S + b * BKV + t_lane;
+      const int kv0 = j * BKV;
+      const bool need_mask = kv0 + BKV > limit;
+      // pass 1: row max
+      float mx = m;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BKV; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c0, v);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + c0 + i < limit) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = ex2_approx((m - m_use) * c);  // m = -inf -> 0
+      // fold in the previous block's P.V while this block's P is still to be written
+      if (j > 0) {
+        ok = mbar_wait(bar_pvfull, (j - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + TM_PV + t_lane + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
+        }
+        tc_fence_before();
+        mbar_arrive(bar_pvempty);
+      }
+      // pass 2: P = exp2(c*(s - m)) -> bf16 -> shared memory (K-major, 128B swizzle)
+      const float mc = m_use * c;
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BKV; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c0, v);
+        tmem_ld_wait();
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = ex2_approx(fmaf(__uint_as_float(v[i]), c, -mc));
+          if (need_mask && !(kv0 + c0 + i < limit)) x = 0.f;
+          e[i] = x;
+          rs += x;
+        }
+        uint8_t* prow = gP + (c0 >> 6) * PANEL + r * 128;
+        const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 pk;
+          pk.x = pack_bf16x2(e[8 * ch + 0], e[8 * ch + 1]);
+          pk.y = pack_bf16x2(e[8 * ch + 2], e[8 * ch + 3]);
+          pk.z = pack_bf16x2(e[8 * ch + 4], e[8 * ch + 5]);
+          pk.w = pack_bf16x2(e[8 * ch + 6], e[8 * ch + 7]);
+          *reinterpret_cast<uint4*>(prow + (((chunk0 + ch) ^ (r & 7)) << 4)) = pk;
+        }
+      }
+      l = l * alpha + rs;
+      m = mx;
+      alpha_prev = alpha;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar_pfull);
+      mbar_arrive(bar_sempty + 8 * b);
+    }
+    if (ok && n_kv > 0) {
+      ok = mbar_wait(bar_pvfull, (n_kv - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + TM_PV + t_lane + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
+        }
+        tc_fence_before();
+      }
+    }
+    if (ok && row < p.Sq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const size_t off = (static_cast<size_t>(bh) * p.Sq + row) * D;
+      if (p.out_bf16) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.O) + off);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          uint4 pk;
+          pk.x = pack_bf16x2(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+          pk.y = pack_bf16x2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+          pk.z = pack_bf16x2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+          pk.w = pack_bf16x2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+          dst[i] = pk;
+        }
+      } else {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.O) + off);
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i)
+          dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv,
+                               o[4 * i + 3] * inv);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
 }
+
+// fp32 -> bf16 (round to nearest even), n4 = element count / 4
+__global__ void f32_to_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst,
+                                   long long n4) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = src[i];
+    dst[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  }
+}
+
+inline size_t pad256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+template <int D>
+kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         const FmhaParams& p, int bh, cudaStream_t stream) {
+  using Cfg = FmhaCfg<D>;
+  static_assert(Cfg::SMEM_TOTAL <= 232448, "shared memory budget");
+  auto kern = fmha_fwd_kernel<D>;
+  KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM_TOTAL));
+  dim3 grid((p.Sq + BQ - 1) / BQ, bh);
+  kern<<<grid, FM_THREADS, Cfg::SMEM_TOTAL, stream>>>(tq, tk, tv, p);
+  g_launches.fetch_add(1);
+  KCG_CUDA_TRY(cudaGetLastError());
+  return KCG_OK;
+}
+
+}  // namespace
+
+size_t fmha_workspace_impl(const kcg_fmha_desc* d) {
+  if (!d || d->dtype_in != KCG_F32) return 0;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0 || d->D <= 0) return 0;
+  const size_t bh = static_cast<size_t>(d->B) * d->H;
+  return pad256(bh * d->Sq * d->D * 2) + 2 * pad256(bh * d->Skv * d->D * 2);
+}
+
+kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void* K, const void* V,
+                              void* O, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (!d || !Q || !K || !V || !O) return KCG_BAD_ARGUMENT;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0) return KCG_BAD_SHAPE;
+  if (d->D != 64 && d->D != 128) return KCG_BAD_SHAPE;
+  if (static_cast<long long>(d->B) * d->H > 65535) return KCG_BAD_SHAPE;
+  if (d->dtype_in != KCG_F32 && d->dtype_in != KCG_BF16) return KCG_UNSUPPORTED;
+  if (d->dtype_out != KCG_F32 && d->dtype_out != KCG_BF16) return KCG_UNSUPPORTED;
+  if (!(d->scale > 0.f)) return KCG_BAD_ARGUMENT;
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return KCG_BAD_ALIGN;
+  const int bh = d->B * d->H;
+  const size_t q_elems = static_cast<size_t>(bh) * d->Sq * d->D;
+  const size_t kv_elems = static_cast<size_t>(bh) * d->Skv * d->D;
+  const void* q = Q;
+  const void* k = K;
+  const void* v = V;
+  if (d->dtype_in == KCG_F32) {
+    const size_t need = fmha_workspace_impl(d);
+    if (!ws || ws_bytes < need || !aligned16(ws)) return KCG_BAD_WORKSPACE;
+    uint8_t* w = static_cast<uint8_t*>(ws);
+    void* qb = w;
+    void* kb = w + pad256(q_elems * 2);
+    void* vb = w + pad256(q_elems * 2) + pad256(kv_elems * 2);
+    const int blocks = device_sm_count() * 4;
+    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(Q),
+                                                    static_cast<uint2*>(qb), q_elems / 4);
+    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(K),
+                                                    static_cast<uint2*>(kb), kv_elems / 4);
+    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(V),
+                                                    static_cast<uint2*>(vb), kv_elems / 4);
+    g_launches.fetch_add(3);
+    KCG_CUDA_TRY(cudaGetLastError());
+    q = qb;
+    k = kb;
+    v = vb;
+  }
+  CUtensorMap tq, tk, tv;
+  const uint32_t box[3] = {64, 128, 1};
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(d->D), static_cast<uint64_t>(d->Sq),
+                              static_cast<uint64_t>(bh)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(d->D) * 2,
+                                 static_cast<uint64_t>(d->Sq) * d->D * 2};
+    kcg_status_t st = encode_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, q, dims, strides, box);
+    if (st != KCG_OK) return st;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(d->D), static_cast<uint64_t>(d->Skv),
+                              static_cast<uint64_t>(bh)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(d->D) * 2,
+                                 static_cast<uint64_t>(d->Skv) * d->D * 2};
+    kcg_status_t st = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, k, dims, strides, box);
+    if (st != KCG_OK) return st;
+    st = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, v, dims, strides, box);
+    if (st != KCG_OK) return st;
+  }
+  FmhaParams p;
+  p.O = O;
+  p.Sq = d->Sq;
+  p.Skv = d->Skv;
+  p.causal = d->causal ? 1 : 0;
+  p.out_bf16 = d->dtype_out == KCG_BF16;
+  p.scale_log2 = d->scale * 1.4426950408889634f;
+  kcg_status_t st = device_status_ptr(&p.status);
+  if (st != KCG_OK) return st;
+  const uint32_t spin = g_spin_limit.load();
+  p.spin = spin ? spin : KCG_SPIN_LIMIT;
+  if (d->D == 64) return launch_fmha<64>(tq, tk, tv, p, bh, stream);
+  return launch_fmha<128>(tq, tk, tv, p, bh, stream);
+}
+
+}  // namespace kcg
