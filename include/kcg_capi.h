@@ -130,6 +130,12 @@ kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const voi
  * its bounded waits runs out; 0 = no timeout.  Synchronises the device. */
 int kcg_last_device_status(void);
 
+/* Self-test of the bounded device-side wait: launches one thread that waits `iterations`
+ * polls (1 .. 2^20) on a barrier nothing arrives on.  Returns KCG_DEVICE_TIMEOUT when the wait
+ * gave up and reported it as designed (the expected outcome), KCG_OK if it did not time out.
+ * The device stays usable afterwards.  No counterpart in the reference (it has no waits). */
+kcg_status_t kcg_selftest_wait_timeout(uint32_t iterations);
+
 /* Test hook: iteration cap of the device-side waits for subsequent launches (0 = default). */
 void kcg_set_spin_limit(uint32_t iterations);
 

@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "kcg_fmha_fwd_host",
     "kcg_last_device_status",
     "kcg_set_spin_limit",
+    "kcg_selftest_wait_timeout",
     "kcg_launch_count",
     "kcg_status_str",
     "kcg_version",
@@ -101,6 +102,8 @@ def load() -> ctypes.CDLL:
     lib.kcg_fmha_fwd_host.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p]
     lib.kcg_last_device_status.restype = c_int
     lib.kcg_last_device_status.argtypes = []
+    lib.kcg_selftest_wait_timeout.restype = c_int
+    lib.kcg_selftest_wait_timeout.argtypes = [c_uint32]
     lib.kcg_set_spin_limit.restype = None
     lib.kcg_set_spin_limit.argtypes = [c_uint32]
     lib.kcg_launch_count.restype = c_uint64

@@ -3,6 +3,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace kcg {
 
@@ -89,6 +90,19 @@ kcg_status_t encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, con
     return KCG_CUDA_ERROR;
   }
   return KCG_OK;
+}
+
+// One thread waits on an mbarrier that nothing ever arrives on: exercises the bounded wait the
+// kernels use (iteration cap -> status word -> clean return) without involving any other unit.
+__global__ void selftest_wait_kernel(int* status, uint32_t limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, DEV_TIMEOUT_EPILOGUE, limit);
+  }
 }
 
 // Host-buffer helper: device buffer that frees itself.
@@ -182,6 +196,19 @@ int kcg_last_device_status(void) {
   if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   if (v != 0) cudaMemset(p, 0, sizeof(int));
   return v;
+}
+
+kcg_status_t kcg_selftest_wait_timeout(uint32_t iterations) {
+  int* status = nullptr;
+  kcg_status_t st = device_status_ptr(&status);
+  if (st != KCG_OK) return st;
+  if (iterations == 0 || iterations > (1u << 20)) return KCG_BAD_ARGUMENT;
+  selftest_wait_kernel<<<1, 32>>>(status, iterations);
+  g_launches.fetch_add(1);
+  KCG_CUDA_TRY(cudaGetLastError());
+  const int v = kcg_last_device_status();
+  if (v < 0) return KCG_CUDA_ERROR;
+  return v == 0 ? KCG_OK : KCG_DEVICE_TIMEOUT;
 }
 
 void kcg_set_spin_limit(uint32_t iterations) { g_spin_limit.store(iterations); }

@@ -63,7 +63,7 @@ void oracle_matmul_f32_mt(const float* A, const float* B, float* C, int64_t m, i
                           int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int threads) {
 #ifdef _OPENMP
   if (threads > 0) omp_set_num_threads(threads);
-#pragma omp parallel for schedule(static)
+#pragma omp parallel for schedule(static) collapse(2)
 #endif
   for (int64_t i = 0; i < m; ++i) {
     for (int64_t j = 0; j < n; ++j) {

@@ -1,0 +1,129 @@
+"""CPU checks of the C-ABI library: it loads without a GPU, exports every symbol the header
+declares, and its argument validation answers before any device work."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from kernelcodegen_b200 import capi
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_functions():
+    text = (ROOT / "include" / "kcg_capi.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(kcg_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(native_lib):
+    names = declared_functions()
+    assert "kcg_gemm_launch" in names and "kcg_fmha_fwd_launch" in names
+    for name in names:
+        assert hasattr(native_lib, name), f"{name} declared in kcg_capi.h but not exported"
+    assert set(capi.EXPORTED_SYMBOLS) <= set(names)
+
+
+def test_struct_sizes_match_header():
+    assert ctypes.sizeof(capi.GemmDesc) == 6 * 8 + 10 * 4 + 8 * 8
+    assert ctypes.sizeof(capi.FmhaDesc) == 10 * 4
+
+
+def test_status_strings(native_lib):
+    assert capi.status_str(capi.KCG_OK) == "KCG_OK"
+    assert capi.status_str(capi.KCG_DEVICE_TIMEOUT) == "KCG_DEVICE_TIMEOUT"
+    assert capi.status_str(12345) == "KCG_UNKNOWN"
+    assert b"sm_100a" in native_lib.kcg_version()
+
+
+def _gemm_desc(m=256, n=256, k=256, prec=capi.KCG_PREC_3XTF32, dt=capi.KCG_F32):
+    d = capi.GemmDesc()
+    d.M, d.N, d.K = m, n, k
+    d.lda, d.ldb, d.ldc = k, n, n
+    d.dtype_in = d.dtype_out = dt
+    d.precision = prec
+    return d
+
+
+def test_workspace_sizes(native_lib):
+    d = _gemm_desc()
+    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 4 * 256 * 256 * 4
+    d = _gemm_desc(prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)
+    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 0
+    f = capi.FmhaDesc()
+    f.B, f.H, f.Sq, f.Skv, f.D = 2, 3, 128, 256, 64
+    f.dtype_in = capi.KCG_F32
+    assert native_lib.kcg_fmha_workspace_bytes(ctypes.byref(f)) == 2 * 3 * 64 * 2 * (128 + 2 * 256)
+    f.dtype_in = capi.KCG_BF16
+    assert native_lib.kcg_fmha_workspace_bytes(ctypes.byref(f)) == 0
+
+
+@pytest.mark.parametrize("mutate,want", [
+    (lambda d: setattr(d, "M", 0), capi.KCG_BAD_SHAPE),
+    (lambda d: setattr(d, "lda", 8), capi.KCG_BAD_SHAPE),
+    (lambda d: setattr(d, "precision", 7), capi.KCG_UNSUPPORTED),
+    (lambda d: setattr(d, "dtype_in", capi.KCG_BF16), capi.KCG_UNSUPPORTED),
+    (lambda d: setattr(d, "epilogue", 5), capi.KCG_UNSUPPORTED),
+    (lambda d: setattr(d, "tile_n", 192), capi.KCG_UNSUPPORTED),
+    (lambda d: setattr(d, "ldc", 258), capi.KCG_BAD_ALIGN),
+    (lambda d: setattr(d, "n_peers", 9), capi.KCG_BAD_ARGUMENT),
+])
+def test_gemm_argument_validation_needs_no_gpu(native_lib, mutate, want):
+    d = _gemm_desc()
+    mutate(d)
+    fake = 0x10000  # never dereferenced: validation fails first
+    st = native_lib.kcg_gemm_launch(ctypes.byref(d), fake, fake, fake, fake, 1 << 30, None)
+    assert st == want, capi.status_str(st)
+
+
+def test_gemm_null_and_misaligned_pointers(native_lib):
+    d = _gemm_desc()
+    assert native_lib.kcg_gemm_launch(None, 16, 16, 16, None, 0, None) == capi.KCG_BAD_ARGUMENT
+    assert native_lib.kcg_gemm_launch(ctypes.byref(d), None, 16, 16, None, 0, None) == capi.KCG_BAD_ARGUMENT
+    assert native_lib.kcg_gemm_launch(ctypes.byref(d), 0x10004, 0x10000, 0x10000, None, 0, None) == capi.KCG_BAD_ALIGN
+    # 3xTF32 needs its scratch
+    assert native_lib.kcg_gemm_launch(ctypes.byref(d), 0x10000, 0x10000, 0x10000, None, 0, None) == capi.KCG_BAD_WORKSPACE
+    assert native_lib.kcg_gemm_launch(ctypes.byref(d), 0x10000, 0x10000, 0x10000, 0x20000, 16, None) == capi.KCG_BAD_WORKSPACE
+
+
+def test_fmha_argument_validation_needs_no_gpu(native_lib):
+    f = capi.FmhaDesc()
+    f.B, f.H, f.Sq, f.Skv, f.D = 1, 1, 128, 128, 64
+    f.dtype_in = f.dtype_out = capi.KCG_BF16
+    f.scale = 1.0
+    fake = 0x10000
+    call = lambda: native_lib.kcg_fmha_fwd_launch(ctypes.byref(f), fake, fake, fake, fake, None, 0, None)
+    f.D = 96
+    assert call() == capi.KCG_BAD_SHAPE
+    f.D = 64
+    f.Skv = 0
+    assert call() == capi.KCG_BAD_SHAPE
+    f.Skv = 128
+    f.scale = 0.0
+    assert call() == capi.KCG_BAD_ARGUMENT
+    f.scale = 1.0
+    f.dtype_in = 3
+    assert call() == capi.KCG_UNSUPPORTED
+    f.dtype_in = capi.KCG_F32  # f32 inputs need scratch for their bf16 copies
+    assert call() == capi.KCG_BAD_WORKSPACE
+    assert native_lib.kcg_fmha_fwd_launch(None, fake, fake, fake, fake, None, 0, None) == capi.KCG_BAD_ARGUMENT
+
+
+def test_ops_refuse_cpu_tensors(native_lib):
+    import torch
+
+    from kernelcodegen_b200 import ops
+
+    a = torch.zeros(128, 128)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.matmul(a, a)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.fmha(torch.zeros(1, 1, 128, 64), torch.zeros(1, 1, 128, 64), torch.zeros(1, 1, 128, 64))
+
+
+def test_product_package_does_not_touch_the_oracle():
+    pkg = ROOT / "kernelcodegen_b200"
+    for path in list(pkg.rglob("*.py")) + list(pkg.rglob("*.cu")) + list(pkg.rglob("*.cuh")):
+        text = path.read_text()
+        assert "oracle" not in text.lower(), f"{path} mentions the oracle"
