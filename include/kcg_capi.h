@@ -126,6 +126,19 @@ kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* h
 kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const void* hK,
                                const void* hV, void* hO);
 
+/* Buffers other ranks' kernels can store into (one process per GPU, same node).  The fused
+ * all-gather of C needs every rank's C buffer mapped into every other rank:
+ *   kcg_peer_alloc  allocates `bytes` of device memory and returns a 64-byte handle that can
+ *                   be sent to the other processes (any byte transport);
+ *   kcg_peer_open   maps a peer's handle into this process and returns a device pointer valid
+ *                   for plain loads/stores from this GPU (peer access is enabled lazily);
+ *   kcg_peer_close / kcg_peer_free undo them.
+ * No counterpart in the reference, which has no multi-GPU path. */
+kcg_status_t kcg_peer_alloc(size_t bytes, void** out_ptr, void* out_handle64);
+kcg_status_t kcg_peer_open(const void* handle64, void** out_ptr);
+kcg_status_t kcg_peer_close(void* ptr);
+kcg_status_t kcg_peer_free(void* ptr);
+
 /* Reads (and clears) the status word of the current device that a kernel sets when one of
  * its bounded waits runs out; 0 = no timeout.  Synchronises the device. */
 int kcg_last_device_status(void);

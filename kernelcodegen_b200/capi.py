@@ -36,6 +36,10 @@ EXPORTED_SYMBOLS = (
     "kcg_fmha_fwd_launch",
     "kcg_gemm_host",
     "kcg_fmha_fwd_host",
+    "kcg_peer_alloc",
+    "kcg_peer_open",
+    "kcg_peer_close",
+    "kcg_peer_free",
     "kcg_last_device_status",
     "kcg_set_spin_limit",
     "kcg_selftest_wait_timeout",
@@ -100,6 +104,14 @@ def load() -> ctypes.CDLL:
     lib.kcg_gemm_host.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p]
     lib.kcg_fmha_fwd_host.restype = c_int
     lib.kcg_fmha_fwd_host.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.kcg_peer_alloc.restype = c_int
+    lib.kcg_peer_alloc.argtypes = [c_size_t, POINTER(c_void_p), c_void_p]
+    lib.kcg_peer_open.restype = c_int
+    lib.kcg_peer_open.argtypes = [c_void_p, POINTER(c_void_p)]
+    lib.kcg_peer_close.restype = c_int
+    lib.kcg_peer_close.argtypes = [c_void_p]
+    lib.kcg_peer_free.restype = c_int
+    lib.kcg_peer_free.argtypes = [c_void_p]
     lib.kcg_last_device_status.restype = c_int
     lib.kcg_last_device_status.argtypes = []
     lib.kcg_selftest_wait_timeout.restype = c_int

@@ -1,5 +1,6 @@
 // extern "C" surface of the library (declared in include/kcg_capi.h) plus the host-side
 // plumbing the launchers share.
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -196,6 +197,44 @@ int kcg_last_device_status(void) {
   if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   if (v != 0) cudaMemset(p, 0, sizeof(int));
   return v;
+}
+
+// ---- peer-visible buffers (fused all-gather) ---------------------------------------------------
+kcg_status_t kcg_peer_alloc(size_t bytes, void** out_ptr, void* out_handle64) {
+  if (!out_ptr || !out_handle64 || bytes == 0) return KCG_BAD_ARGUMENT;
+  void* p = nullptr;
+  KCG_CUDA_TRY(cudaMalloc(&p, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "kcg: cudaIpcGetMemHandle failed: %s\n", cudaGetErrorString(e));
+    cudaFree(p);
+    return KCG_CUDA_ERROR;
+  }
+  static_assert(sizeof(h) == 64, "IPC handle is 64 bytes");
+  std::memcpy(out_handle64, &h, 64);
+  *out_ptr = p;
+  return KCG_OK;
+}
+
+kcg_status_t kcg_peer_open(const void* handle64, void** out_ptr) {
+  if (!handle64 || !out_ptr) return KCG_BAD_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, 64);
+  KCG_CUDA_TRY(cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return KCG_OK;
+}
+
+kcg_status_t kcg_peer_close(void* ptr) {
+  if (!ptr) return KCG_BAD_ARGUMENT;
+  KCG_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return KCG_OK;
+}
+
+kcg_status_t kcg_peer_free(void* ptr) {
+  if (!ptr) return KCG_BAD_ARGUMENT;
+  KCG_CUDA_TRY(cudaFree(ptr));
+  return KCG_OK;
 }
 
 kcg_status_t kcg_selftest_wait_timeout(uint32_t iterations) {
