@@ -37,7 +37,8 @@ typedef enum kcg_status_t {
   KCG_PEER_TIMEOUT = 6,   /* host-side check-in of the ranks timed out                      */
   KCG_NCCL_ERROR = 7,
   KCG_BAD_WORKSPACE = 8,  /* workspace NULL or smaller than kcg_*_workspace_bytes()         */
-  KCG_BAD_ARGUMENT = 9    /* NULL descriptor / NULL tensor pointer                          */
+  KCG_BAD_ARGUMENT = 9,   /* NULL descriptor / NULL tensor pointer                          */
+  KCG_TOO_LARGE = 10      /* problem needs more scratch than kcg_gemm_launch_static holds   */
 } kcg_status_t;
 
 typedef enum kcg_dtype_t { KCG_F32 = 0, KCG_BF16 = 1 } kcg_dtype_t;
@@ -112,6 +113,30 @@ size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d);
  * (src/Backend/CUDA.cc:773-857) for the scheduled Matmul func, with Relu fused. */
 kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same fp32-contract (3xTF32) matmul(+ReLU) as kcg_gemm_launch, for callers that cannot hand
+ * over a workspace because they cannot allocate device memory at all: a plug-in running inside
+ * a host whose allocator has reserved the whole GPU up front (a cudaMalloc there fails or
+ * fragments the host's pool), or a latency-critical loop where an allocation's implicit
+ * device synchronisation is not acceptable.  The hi/lo split copies of A and B go into a
+ * fixed array that is part of the library image, KCG_STATIC_SCRATCH_BYTES (32 MiB) on every
+ * GPU that loads the library, held until the process exits.  This call performs no
+ * cudaMalloc/cudaFree and calls nothing that allocates.
+ *   - Limit: kcg_gemm_workspace_bytes(d) <= KCG_STATIC_SCRATCH_BYTES, i.e.
+ *     8*(M*K + K*N) bytes (each term rounded up to 256) -- e.g. up to 1024 x N x 1024 with
+ *     N <= 3072.  Larger problems return KCG_TOO_LARGE (and say so on stderr).
+ *   - Only precision KCG_PREC_3XTF32 (the one path that needs scratch); others:
+ *     KCG_UNSUPPORTED -- use kcg_gemm_launch with a NULL workspace for those.
+ *   - The first call on each device looks up the array's device address; make that first
+ *     call before starting any stream capture on that device.
+ *   - All calls on a device share the one array.  Nothing in it has to be cleared between
+ *     calls (each call rewrites every byte it later reads), but two calls whose kernels
+ *     overlap on the GPU (different streams, no ordering between them) race on it: keep
+ *     calls to this entry point ordered on one stream, or serialise them yourself.
+ * This entry point has no counterpart in the reference. */
+#define KCG_STATIC_SCRATCH_BYTES (32u << 20)
+kcg_status_t kcg_gemm_launch_static(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                                    void* stream);
 
 /* Replaces: launch of `Fused_Multi_Head_Attention_*::kernel0(Q, K, V, O)`
  * (src/Optimizer/Optimizer.cc:1101-1111, src/Backend/CUDA.cc:773-857). */

@@ -22,6 +22,8 @@ KCG_PEER_TIMEOUT = 6
 KCG_NCCL_ERROR = 7
 KCG_BAD_WORKSPACE = 8
 KCG_BAD_ARGUMENT = 9
+KCG_TOO_LARGE = 10
+KCG_STATIC_SCRATCH_BYTES = 32 << 20
 
 # enum kcg_dtype_t / kcg_precision_t / kcg_epilogue_t / kcg_layout_t
 KCG_F32, KCG_BF16 = 0, 1
@@ -33,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "kcg_gemm_workspace_bytes",
     "kcg_fmha_workspace_bytes",
     "kcg_gemm_launch",
+    "kcg_gemm_launch_static",
     "kcg_fmha_fwd_launch",
     "kcg_gemm_host",
     "kcg_fmha_fwd_host",
@@ -98,6 +101,8 @@ def load() -> ctypes.CDLL:
     lib.kcg_fmha_workspace_bytes.argtypes = [POINTER(FmhaDesc)]
     lib.kcg_gemm_launch.restype = c_int
     lib.kcg_gemm_launch.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.kcg_gemm_launch_static.restype = c_int
+    lib.kcg_gemm_launch_static.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p]
     lib.kcg_fmha_fwd_launch.restype = c_int
     lib.kcg_fmha_fwd_launch.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
     lib.kcg_gemm_host.restype = c_int

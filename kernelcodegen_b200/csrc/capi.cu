@@ -130,6 +130,11 @@ kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* 
                           static_cast<cudaStream_t>(stream));
 }
 
+kcg_status_t kcg_gemm_launch_static(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                                    void* stream) {
+  return gemm_launch_static_impl(d, A, B, C, static_cast<cudaStream_t>(stream));
+}
+
 kcg_status_t kcg_fmha_fwd_launch(const kcg_fmha_desc* d, const void* Q, const void* K,
                                  const void* V, void* O, void* workspace, size_t workspace_bytes,
                                  void* stream) {
@@ -266,6 +271,7 @@ const char* kcg_status_str(kcg_status_t s) {
     case KCG_NCCL_ERROR: return "KCG_NCCL_ERROR";
     case KCG_BAD_WORKSPACE: return "KCG_BAD_WORKSPACE";
     case KCG_BAD_ARGUMENT: return "KCG_BAD_ARGUMENT";
+    case KCG_TOO_LARGE: return "KCG_TOO_LARGE";
   }
   return "KCG_UNKNOWN";
 }

@@ -39,6 +39,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                               void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t gemm_workspace_impl(const kcg_gemm_desc* d);
+kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                                     cudaStream_t stream);
 kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void* K, const void* V,
                               void* O, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t fmha_workspace_impl(const kcg_fmha_desc* d);

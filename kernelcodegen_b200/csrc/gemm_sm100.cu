@@ -18,12 +18,21 @@
 // Precisions (KIND): 0 = bf16 inputs, 1 = single TF32 product of fp32 inputs,
 // 2 = 3xTF32: four operand tiles per stage (A_hi, A_lo, B_hi, B_lo) and three UMMA passes
 //     a_lo*b_hi + a_hi*b_lo + a_hi*b_hi accumulated in fp32.
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace kcg {
 
 namespace {
+
+// Scratch of the entry point that allocates nothing (kcg_gemm_launch_static): the hi/lo split
+// copies of A and B live here instead of in a caller-provided workspace.  Every device that
+// loads the library holds these bytes until the process exits.  In host code this name is only
+// a stand-in for the symbol; the device address is looked up with cudaGetSymbolAddress.
+constexpr size_t STATIC_SCRATCH_BYTES = KCG_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
 constexpr int BM = 128;
 constexpr int GEMM_THREADS = 192;
@@ -514,6 +523,47 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   }
   if (kind == 1) return dispatch_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
   return dispatch_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+}
+
+// Device address of g_static_scratch on the current device.  Looked up once per device, with
+// that device current (the symbol has one instance per device).
+static kcg_status_t static_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static void* cache[64] = {};
+  int dev = 0;
+  KCG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KCG_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    KCG_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (!p) return KCG_CUDA_ERROR;
+    cache[dev] = p;
+  }
+  *out = cache[dev];
+  return KCG_OK;
+}
+
+kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                                     cudaStream_t stream) {
+  if (!d) return KCG_BAD_ARGUMENT;
+  if (d->precision != KCG_PREC_3XTF32) return KCG_UNSUPPORTED;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
+  const size_t need = gemm_workspace_impl(d);
+  if (need > STATIC_SCRATCH_BYTES) {
+    std::fprintf(stderr,
+                 "kcg: kcg_gemm_launch_static: %lld x %lld x %lld needs %zu bytes of scratch, the "
+                 "built-in scratch holds %zu; use kcg_gemm_launch with a workspace\n",
+                 static_cast<long long>(d->M), static_cast<long long>(d->N),
+                 static_cast<long long>(d->K), need, STATIC_SCRATCH_BYTES);
+    return KCG_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  kcg_status_t st = static_scratch_ptr(&scratch);
+  if (st != KCG_OK) return st;
+  // The split pass overwrites every byte of scratch the GEMM then reads, so nothing left by an
+  // earlier call is ever consumed and nothing has to be cleared.
+  return gemm_launch_impl(d, A, B, C, scratch, STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // namespace kcg
