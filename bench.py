@@ -429,6 +429,21 @@ def run_ours(args):
     flops = 2.0 * M * N * K
     value = flops / ms_step / 1e9
 
+    # all-gather check (outside the timed region): the first 128 rows of the next rank's block, as
+    # they arrived in THIS rank's copy of C, against a local recomputation from the same seed
+    allgather_check = None
+    if dist is not None:
+        nxt = (rank + 1) % world
+        plo, phi = sharding.row_block(M, nxt, world)
+        g2 = torch.Generator(device=dev)
+        g2.manual_seed(40 * 100003 + plo)
+        a_peer = (torch.randn((min(chunk, phi - plo), K), generator=g2, device=dev) * 0.02).bfloat16()[:128]
+        want = ops.matmul_relu(a_peer.contiguous(), b)
+        diff = (c_full[plo:plo + 128].float() - want.float()).abs().max()
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        allgather_check = {"rows_checked_per_rank": 128, "max_abs_diff": float(diff.item())}
+        del a_peer, want
+
     # kernel-only duration (no barrier): CUDA events around the GEMM launch alone
     def gemm_only():
         ops.matmul_relu(a, b, out=c_local, peers=peers)
@@ -500,6 +515,8 @@ def run_ours(args):
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches_timed, "clocks": clocks,
             "device_status": [status, status2], "others": others,
         }
+        if allgather_check is not None:
+            line["allgather_check"] = allgather_check
         if tf32_peak is not None:
             line["tf32_cublas_tflops_live"] = tf32_peak
         if cpu is not None:
