@@ -353,6 +353,10 @@ def fmha_long(torch, dev, peaks, ops, bh_lo, bh_hi, dist=None, steps=5):
 
 
 def run_ours(args):
+    # Keep stdout for the one JSON line: anything a library prints to fd 1 (NCCL's version
+    # banner, for instance) goes to stderr instead.
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     import torch
 
     rank = int(os.environ.get("RANK", "0"))
@@ -521,7 +525,7 @@ def run_ours(args):
             line["tf32_cublas_tflops_live"] = tf32_peak
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line), flush=True)
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

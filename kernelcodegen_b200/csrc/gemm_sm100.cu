@@ -60,7 +60,8 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = NOPS * (A_BYTES + B_BYTES);
   static constexpr int CTRL_BYTES = 1024;            // barriers, TMEM pointer, abort flag
-  static constexpr int MAX_STAGES = (SMEM_LIMIT - CTRL_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int EPI_BYTES = 4 * 4096;         // one 32-row x 128-byte staging slab per epilogue warp
+  static constexpr int MAX_STAGES = (SMEM_LIMIT - CTRL_BYTES - EPI_BYTES - 1024) / STAGE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;           // two accumulator buffers (256 or 512)
 };
 
@@ -249,6 +250,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ------------------------------- epilogue (4 warps) --------------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* epi_stage = ctrl + Cfg::CTRL_BYTES + q * 4096;  // this warp's 32 x 128 B slab
     int local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
@@ -260,54 +262,80 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                      p.spin);
       if (!ok) break;
       tc_fence_after();
-      const int row = mb * BM + q * 32 + lane;
+      const int row0 = mb * BM + q * 32;           // first row of this warp's 32-row slab
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      // Each pass handles CW columns = 128 bytes of output per row: thread t (row t of the
+      // slab) packs its part into the warp's staging slab [32 rows x 128 B] (16-byte chunks
+      // XOR-swizzled by row against bank conflicts); the warp then writes the slab out with
+      // 8 lanes per row, so every store instruction covers four full 128-byte row segments.
+      constexpr int CW = 128 / static_cast<int>(sizeof(OutT));   // 64 bf16 or 32 fp32 columns
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += CW) {
         const int col = nb * BN + c0;
         if (col >= p.N) break;
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c0, r);
-        tmem_ld_wait();
-        if (p.relu) {
+        const bool full = (col + CW <= p.N);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = (r[i] & 0x80000000u) ? 0u : r[i];
-        }
-        if (row < p.M) {
-          const long long off = static_cast<long long>(row) * p.ldc + col;
-          if (sizeof(OutT) == 2) {
-            uint32_t pk[16];
+        for (int sub = 0; sub < CW / 32; ++sub) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c0 + sub * 32, r);
+          tmem_ld_wait();
+          if (p.relu) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-            for (int dst = 0; dst <= p.n_peers; ++dst) {
-              OutT* cp = static_cast<OutT*>(dst == 0 ? p.C : p.peers[dst - 1]) + off;
-              if (col + 32 <= p.N) {
-                uint4* v = reinterpret_cast<uint4*>(cp);
+            for (int i = 0; i < 32; ++i) r[i] = (r[i] & 0x80000000u) ? 0u : r[i];
+          }
+          if (full) {
+            uint8_t* srow = epi_stage + lane * 128;
+            if (sizeof(OutT) == 2) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  v[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-              } else {
-                unsigned short* s = reinterpret_cast<unsigned short*>(cp);
-                for (int i = 0; i < 32 && col + i < p.N; ++i)
-                  s[i] = static_cast<unsigned short>((i & 1) ? (pk[i >> 1] >> 16)
-                                                             : (pk[i >> 1] & 0xFFFFu));
+              for (int ch = 0; ch < 4; ++ch) {  // 8 bf16 per 16-byte chunk
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                *reinterpret_cast<uint4*>(srow + (((sub * 4 + ch) ^ (lane & 7)) << 4)) = v;
               }
+            } else {
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch)    // 4 fp32 per 16-byte chunk
+                *reinterpret_cast<uint4*>(srow + ((ch ^ (lane & 7)) << 4)) =
+                    make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
             }
-          } else {
+          } else if (row0 + lane < p.M) {
+            // ragged right edge: element-wise, this thread's row
+            const long long off = static_cast<long long>(row0 + lane) * p.ldc + col + sub * 32;
             for (int dst = 0; dst <= p.n_peers; ++dst) {
               OutT* cp = static_cast<OutT*>(dst == 0 ? p.C : p.peers[dst - 1]) + off;
-              if (col + 32 <= p.N) {
-                uint4* v = reinterpret_cast<uint4*>(cp);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  v[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-              } else {
-                uint32_t* s = reinterpret_cast<uint32_t*>(cp);
-                for (int i = 0; i < 32 && col + i < p.N; ++i) s[i] = r[i];
+              for (int i = 0; i < 32; ++i) {
+                if (col + sub * 32 + i < p.N) {
+                  if (sizeof(OutT) == 2)
+                    reinterpret_cast<__nv_bfloat16*>(cp)[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+                  else
+                    reinterpret_cast<uint32_t*>(cp)[i] = r[i];
+                }
               }
             }
           }
+        }
+        if (full) {
+          __syncwarp();
+          const int rr = lane >> 3, ch = lane & 7;
+          for (int dst = 0; dst <= p.n_peers; ++dst) {
+            uint8_t* cbase = static_cast<uint8_t*>(dst == 0 ? p.C : p.peers[dst - 1]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rloc = i * 4 + rr;
+              const int grow = row0 + rloc;
+              if (grow < p.M) {
+                const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
+                                                                 ((ch ^ (rloc & 7)) << 4));
+                *reinterpret_cast<uint4*>(cbase + (static_cast<long long>(grow) * p.ldc + col) *
+                                                      static_cast<long long>(sizeof(OutT)) +
+                                          ch * 16) = v;
+              }
+            }
+          }
+          __syncwarp();
         }
       }
       tc_fence_before();
@@ -360,7 +388,7 @@ kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const
   static_assert(STAGES >= 2, "need at least two pipeline stages");
   if (stages_req != 0 && stages_req != STAGES) return KCG_UNSUPPORTED;
   auto kern = gemm_kernel<KIND, BN, STAGES, B_KMAJOR, OutT>;
-  constexpr int smem = STAGES * Cfg::STAGE_BYTES + Cfg::CTRL_BYTES + 1024;
+  constexpr int smem = STAGES * Cfg::STAGE_BYTES + Cfg::CTRL_BYTES + Cfg::EPI_BYTES + 1024;
   static_assert(smem <= SMEM_LIMIT, "shared memory budget");
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int sms = device_sm_count();
