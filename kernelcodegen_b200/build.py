@@ -74,6 +74,49 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+HOST_LIB_PATH = PKG_DIR / "libkcg_runtime.so"
+ROOT = PKG_DIR.parent
+
+
+def host_sources() -> list[Path]:
+    return sorted((ROOT / "src").rglob("*.cc"))
+
+
+def build_host(force: bool = False) -> Path:
+    """Compile the C++ operator API (include/, src/) into libkcg_runtime.so, linked against the
+    kernel library.  Plain g++; no CUDA headers are needed on this side of the C-ABI."""
+    build(force=False)
+    deps = host_sources() + list((ROOT / "include").rglob("*.h"))
+    if not force and HOST_LIB_PATH.exists():
+        t = HOST_LIB_PATH.stat().st_mtime
+        if all(p.stat().st_mtime <= t for p in deps) and LIB_PATH.stat().st_mtime <= t:
+            return HOST_LIB_PATH
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    tmp = HOST_LIB_PATH.with_suffix(".so.tmp")
+    cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-I", str(ROOT / "include"),
+           *map(str, host_sources()), "-o", str(tmp), "-L", str(PKG_DIR), "-lkcg_b200",
+           "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout)
+        raise RuntimeError("building libkcg_runtime.so failed")
+    os.replace(tmp, HOST_LIB_PATH)
+    return HOST_LIB_PATH
+
+
+def compile_program(source: Path, output: Path, extra: list[str] | None = None) -> Path:
+    """Compile a user program against the operator API (used by the C++ tests/examples)."""
+    build_host()
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-std=c++17", "-O1", "-I", str(ROOT / "include"), str(source), "-o", str(output),
+           "-L", str(PKG_DIR), "-lkcg_runtime", "-lkcg_b200", f"-Wl,-rpath,{PKG_DIR}", *(extra or [])]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"compiling {source} failed:\n{res.stdout}")
+    return output
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_host(force="--force" in sys.argv))
