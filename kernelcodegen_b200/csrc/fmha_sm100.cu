@@ -1,18 +1,28 @@
-// O = softmax(scale * Q.K^T [causal]) . V on sm_100a, one CTA per (batch*head, 128-query tile).
+// O = softmax(scale * Q.K^T [causal]) . V on sm_100a; one CTA per (batch*head, 256 queries).
 //
 // The computation is the reference's three-operator graph (test/test.cc:88-90):
 // BatchedMatmul(Q, K colMajor) (src/Frontend/Operators.cc:353-414), Softmax over the last axis
 // (:474-536) and BatchedMatmul(P, V).  The reference's FMHAOptimizer fuses that chain into a
 // FlashAttention-2 style kernel with scalar FFMA outer products and shuffle reductions
 // (src/Optimizer/Optimizer.cc:1079-1333); here both contractions run on tcgen05 tensor cores
-// and the online softmax works on rows read straight out of TMEM:
+// and the online softmax works on rows read straight out of TMEM.
 //
-//   warp 0      TMA producer : Q once, then K_j / V_j blocks (128 keys) through 2-stage rings
-//   warp 1      UMMA issuer  : S_j = Q.K_j^T -> TMEM (two S buffers), O_j = P_j.V_j -> TMEM
-//   warps 2..5  softmax      : thread t owns query row t: tcgen05.ld its S row, running max /
-//                              sum (thread-local: one row never spans lanes in this TMEM
-//                              layout), P_j = exp2(...) as bf16 into swizzled shared memory,
-//                              O += rescaled P_j.V_j in registers, final O / l -> global
+// A CTA owns two 128-query tiles that share every K_j / V_j block (128 keys) it loads:
+//
+//   warp 0        TMA producer : Q tiles once, then K_j / V_j through 2-stage rings
+//   warp 1        UMMA issuer  : per block j and tile t: S_t = Q_t.K_j^T -> TMEM, then, once the
+//                                softmax warps have turned S_t into P_t in place (bf16, same
+//                                TMEM columns), PV_t = P_t.V_j -> TMEM with P_t as the TMEM
+//                                operand.  Issue order PV_0(j), S_0(j+1), PV_1(j), S_1(j+1) keeps
+//                                the tensor core busy with one tile while the other tile's
+//                                softmax runs.
+//   warps 4..7    softmax, tile 0 } thread t owns query row t of its tile: tcgen05.ld of its S
+//   warps 8..11   softmax, tile 1 } row (pass 1: running max; pass 2: exp2 -> P), running sum,
+//                                   O += rescaled PV_t in registers, final O / l -> global.
+//
+// Row max / row sum are thread-local (one TMEM lane = one query row), so no cross-lane step
+// exists.  Registers are re-balanced with setmaxnreg: the softmax warpgroups hold an O row of D
+// floats per thread, the producer/issuer warpgroup needs next to nothing.
 //
 // Online softmax: m_j = max(m_{j-1}, rowmax(S_j)), alpha_j = exp(scale*(m_{j-1}-m_j)),
 // l_j = alpha_j*l_{j-1} + rowsum(P_j), O_j = alpha_j*O_{j-1} + P_j.V_j, out = O_n / l_n --
@@ -25,9 +35,10 @@ namespace kcg {
 
 namespace {
 
-constexpr int FM_THREADS = 192;
-constexpr int BQ = 128;   // query rows per CTA
-constexpr int BKV = 128;  // keys per block
+constexpr int FM_THREADS = 384;
+constexpr int BQ = 128;        // query rows per tile
+constexpr int QTILES = 2;      // tiles per CTA
+constexpr int BKV = 128;       // keys per block
 
 struct FmhaParams {
   void* O;
@@ -41,13 +52,24 @@ struct FmhaParams {
 
 template <int D>
 struct FmhaCfg {
-  static constexpr int TILE_BYTES = 128 * D * 2;      // Q, K_j, V_j tile: 128 rows x D bf16
+  static constexpr int TILE_BYTES = 128 * D * 2;      // Q_t, K_j, V_j tile: 128 rows x D bf16
   static constexpr int PANEL_BYTES = 128 * 128;       // 128 rows x 64 bf16 (one swizzle panel)
-  static constexpr int P_BYTES = BQ * BKV * 2;        // 32 KB
-  static constexpr int SMEM_DATA = TILE_BYTES /*Q*/ + 2 * TILE_BYTES /*K*/ + 2 * TILE_BYTES /*V*/ + P_BYTES;
+  static constexpr int SMEM_DATA = QTILES * TILE_BYTES + 2 * TILE_BYTES /*K*/ + 2 * TILE_BYTES /*V*/;
   static constexpr int SMEM_TOTAL = SMEM_DATA + 1024 /*ctrl*/ + 1024 /*align slack*/;
-  static constexpr int TMEM_COLS = 512;               // S0 | S1 | PV
+  static constexpr int TMEM_COLS = 512;               // S0 | S1 | PV0 | PV1
 };
+
+// Register re-balancing.  The CTA is launched with 384 threads x 168 registers = 64512; the
+// pool never grows, so after the change the three warpgroups must still fit in 64512:
+// 128 x 40 + 256 x 232 = 64512 exactly.  (setmaxnreg.inc waits, unbounded, for registers to be
+// released -- a budget that does not add up hangs the CTA.)
+static_assert(128 * 40 + 256 * 232 <= 384 * 168, "setmaxnreg budget must fit the launch allocation");
+__device__ __forceinline__ void reg_dealloc_40() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+}
+__device__ __forceinline__ void reg_alloc_232() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
+}
 
 template <int D>
 __global__ void __launch_bounds__(FM_THREADS, 1)
@@ -59,29 +81,25 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int DPANELS = D / 64;
   constexpr uint32_t IDESC_S = make_idesc(UMMA_FMT_BF16, BQ, BKV, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc(UMMA_FMT_BF16, BQ, D, 0, 1);
-  constexpr uint32_t TM_S = 0, TM_PV = 256;
+  constexpr uint32_t TM_S = 0, TM_PV = 256;           // + 128 * tile
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw);
-  const uint32_t sQ = base;
-  const uint32_t sK = sQ + TILE;
-  const uint32_t sV = sK + 2 * TILE;
-  const uint32_t sP = sV + 2 * TILE;
-  uint8_t* gP = gen_base + 5 * TILE;
-  const uint32_t ctrl_u = sP + Cfg::P_BYTES;
+  const uint32_t sQ = base;                           // [QTILES]
+  const uint32_t sK = sQ + QTILES * TILE;             // [2]
+  const uint32_t sV = sK + 2 * TILE;                  // [2]
+  const uint32_t ctrl_u = sV + 2 * TILE;
   uint8_t* ctrl = gen_base + Cfg::SMEM_DATA;
-  const uint32_t bar_q = ctrl_u;
-  const uint32_t bar_kfull = ctrl_u + 8;     // [2]
-  const uint32_t bar_kempty = ctrl_u + 24;   // [2]
-  const uint32_t bar_vfull = ctrl_u + 40;    // [2]
-  const uint32_t bar_vempty = ctrl_u + 56;   // [2]
-  const uint32_t bar_sfull = ctrl_u + 72;    // [2]
-  const uint32_t bar_sempty = ctrl_u + 88;   // [2]
-  const uint32_t bar_pfull = ctrl_u + 104;
-  const uint32_t bar_pvfull = ctrl_u + 112;
-  const uint32_t bar_pvempty = ctrl_u + 120;
+  const uint32_t bar_q = ctrl_u;             // [2] one per tile
+  const uint32_t bar_kfull = ctrl_u + 16;    // [2]
+  const uint32_t bar_kempty = ctrl_u + 32;   // [2]
+  const uint32_t bar_vfull = ctrl_u + 48;    // [2]
+  const uint32_t bar_vempty = ctrl_u + 64;   // [2]
+  const uint32_t bar_sfull = ctrl_u + 80;    // [2] per tile: S_t(j) complete in TMEM
+  const uint32_t bar_pfull = ctrl_u + 96;    // [2] per tile: P_t(j) written, PV_t(j-1) consumed
+  const uint32_t bar_pvfull = ctrl_u + 112;  // [2] per tile: PV_t(j) complete in TMEM
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(ctrl + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 132);
 
@@ -89,33 +107,37 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
   // heavy (late) query tiles first when causal
-  const int qt = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int q0 = qt * BQ;
+  const int qpair = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int q0 = qpair * (QTILES * BQ);
   const int shift = p.Skv - p.Sq;  // causal: query i sees keys j <= i + shift
-  int kv_end = p.Skv;
-  if (p.causal) {
-    const int lim = q0 + BQ + shift;  // exclusive bound for the last row of the tile
-    kv_end = lim < kv_end ? lim : kv_end;
-    if (kv_end < 0) kv_end = 0;
+  // number of key blocks tile t needs (0 when the tile starts beyond Sq)
+  int n_kv_t[QTILES];
+#pragma unroll
+  for (int t = 0; t < QTILES; ++t) {
+    int kv_end = p.Skv;
+    if (p.causal) {
+      const int lim = q0 + (t + 1) * BQ + shift;  // exclusive bound for the last row of the tile
+      kv_end = lim < kv_end ? lim : kv_end;
+      if (kv_end < 0) kv_end = 0;
+    }
+    n_kv_t[t] = (q0 + t * BQ < p.Sq) ? (kv_end + BKV - 1) / BKV : 0;
   }
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int n_kv = n_kv_t[0] > n_kv_t[1] ? n_kv_t[0] : n_kv_t[1];
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    mbar_init(bar_q, 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_q + 8 * i, 1);
       mbar_init(bar_kfull + 8 * i, 1);
       mbar_init(bar_kempty + 8 * i, 1);
       mbar_init(bar_vfull + 8 * i, 1);
       mbar_init(bar_vempty + 8 * i, 1);
       mbar_init(bar_sfull + 8 * i, 1);
-      mbar_init(bar_sempty + 8 * i, 128);
+      mbar_init(bar_pfull + 8 * i, 128);
+      mbar_init(bar_pvfull + 8 * i, 1);
     }
-    mbar_init(bar_pfull, 128);
-    mbar_init(bar_pvfull, 1);
-    mbar_init(bar_pvempty, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -128,12 +150,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
-    // ------------------------------- TMA producer -------------------------------------------
-    if (lane == 0 && n_kv > 0) {
-      mbar_expect_tx(bar_q, TILE);
+  if (warp < 4) {
+    reg_dealloc_40();
+    if (warp == 0 && lane == 0 && n_kv > 0) {
+      // ------------------------------- TMA producer -----------------------------------------
 #pragma unroll
-      for (int dp = 0; dp < DPANELS; ++dp) tma_load_3d(sQ + dp * PANEL, &tmQ, bar_q, dp * 64, q0, bh);
+      for (int t = 0; t < QTILES; ++t) {
+        if (n_kv_t[t] == 0) continue;
+        mbar_expect_tx(bar_q + 8 * t, TILE);
+#pragma unroll
+        for (int dp = 0; dp < DPANELS; ++dp)
+          tma_load_3d(sQ + t * TILE + dp * PANEL, &tmQ, bar_q + 8 * t, dp * 64, q0 + t * BQ, bh);
+      }
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int b = j & 1;
@@ -153,72 +181,98 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (!ok) {
         // give copies already in flight time to land before shared memory is released
-        for (uint32_t it = 0; it < 4096u; ++it) {
-          if (mbar_try_wait(bar_q, 0)) break;
-        }
-        for (int b = 0; b < 2; ++b)
+        for (int i = 0; i < 2; ++i)
           for (uint32_t it = 0; it < 4096u; ++it) {
-            if (mbar_try_wait(bar_kfull + 8 * b, 0) | mbar_try_wait(bar_vfull + 8 * b, 0)) break;
+            if (mbar_try_wait(bar_q + 8 * i, 0) & mbar_try_wait(bar_kfull + 8 * i, 0) &
+                mbar_try_wait(bar_vfull + 8 * i, 0))
+              break;
           }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------- UMMA issuer ---------------------------------------------
-    if (lane == 0 && n_kv > 0) {
-      bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, DEV_TIMEOUT_Q, p.spin);
-      auto issue_s = [&](int j) -> bool {
-        const int b = j & 1;
-        const uint32_t par = (j >> 1) & 1u;
-        if (!mbar_wait(bar_kfull + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin))
-          return false;
-        if (!mbar_wait(bar_sempty + 8 * b, par ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM,
-                       p.spin))
-          return false;
-        tc_fence_after();
-        const uint32_t kb = sK + b * TILE;
+    } else if (warp == 1 && lane == 0 && n_kv > 0) {
+      // ------------------------------- UMMA issuer -------------------------------------------
+      bool ok = true;
+      auto issue_s = [&](int t, int j) {
+        // S_t(j) = Q_t . K_j^T; the caller has waited for K_j and for the S_t buffer
+        const uint32_t kb = sK + (j & 1) * TILE;
+        const uint32_t qb = sQ + t * TILE;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S + b * BKV, make_smem_desc(sQ + off, 16, 1024),
+          umma_bf16_ss(tmem_base + TM_S + t * BKV, make_smem_desc(qb + off, 16, 1024),
                        make_smem_desc(kb + off, 16, 1024), IDESC_S, ks ? 1u : 0u);
         }
-        umma_commit(bar_kempty + 8 * b);
-        umma_commit(bar_sfull + 8 * b);
-        return true;
+        umma_commit(bar_sfull + 8 * t);
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          ok = issue_s(j + 1);
-          if (!ok) break;
-        }
-        const int b = j & 1;
-        ok = mbar_wait(bar_vfull + 8 * b, (j >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL,
-                       p.spin) &&
-             mbar_wait(bar_pvempty, (j & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM,
-                       p.spin) &&
-             mbar_wait(bar_pfull, j & 1u, abort_flag, p.status, DEV_TIMEOUT_P, p.spin);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t vb = sV + b * TILE;
+      auto issue_pv = [&](int t, int j) {
+        // PV_t(j) = P_t(j) . V_j with P_t in the TMEM columns of S_t (16 keys = 8 columns)
+        const uint32_t vb = sV + (j & 1) * TILE;
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks) {
-          const uint64_t pd = make_smem_desc(sP + (ks >> 2) * PANEL + (ks & 3) * 32, 16, 1024);
-          // V tile: D/64 groups of [128 keys x 128 bytes]; 16 keys = 2048 bytes
           const uint64_t vd = make_smem_desc(vb + ks * 2048, PANEL, 1024);
-          umma_bf16_ss(tmem_base + TM_PV, pd, vd, IDESC_PV, ks ? 1u : 0u);
+          umma_bf16_ts(tmem_base + TM_PV + t * 128, tmem_base + TM_S + t * BKV + ks * 8, vd, IDESC_PV,
+                       ks ? 1u : 0u);
         }
+        umma_commit(bar_pvfull + 8 * t);
+      };
+      // prologue: S_0(0), S_1(0)
+#pragma unroll
+      for (int t = 0; t < QTILES && ok; ++t) {
+        if (n_kv_t[t] == 0) continue;
+        ok = mbar_wait(bar_q + 8 * t, 0, abort_flag, p.status, DEV_TIMEOUT_Q, p.spin);
+        if (ok && t == 0)
+          ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin);
+        if (ok && t == 1 && n_kv_t[0] == 0)
+          ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(t, 0);
+      }
+      if (ok) umma_commit(bar_kempty);  // K_0 is free once S_0(0), S_1(0) have read it
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t par = (j >> 1) & 1u;
+        const bool next = j + 1 < n_kv;
+        bool k_next_ready = false;
+#pragma unroll
+        for (int t = 0; t < QTILES && ok; ++t) {
+          if (j < n_kv_t[t]) {
+            if (t == 0 || j >= n_kv_t[0]) {
+              ok = mbar_wait(bar_vfull + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin);
+              if (!ok) break;
+            }
+            ok = mbar_wait(bar_pfull + 8 * t, j & 1u, abort_flag, p.status, DEV_TIMEOUT_P, p.spin);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, j);
+          }
+          if (next && j + 1 < n_kv_t[t]) {
+            if (!k_next_ready) {
+              ok = mbar_wait(bar_kfull + 8 * (b ^ 1), ((j + 1) >> 1) & 1u, abort_flag, p.status,
+                             DEV_TIMEOUT_MMA_FULL, p.spin);
+              if (!ok) break;
+              k_next_ready = true;
+              tc_fence_after();
+            }
+            issue_s(t, j + 1);
+          }
+        }
+        if (!ok) break;
         umma_commit(bar_vempty + 8 * b);
-        umma_commit(bar_pvfull);
+        if (next) umma_commit(bar_kempty + 8 * (b ^ 1));
       }
     }
   } else {
-    // ------------------------------- softmax / output (4 warps) ------------------------------
-    const int q = warp & 3;
+    // ------------------------------- softmax / output (2 x 4 warps) --------------------------
+    reg_alloc_232();
+    const int t = (warp >> 2) - 1;        // tile of this warpgroup
+    const int q = warp & 3;               // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;          // row inside the tile == TMEM lane
-    const int row = q0 + r;               // query index
+    const int row = q0 + t * BQ + r;      // query index
     const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t t_s = tmem_base + TM_S + t * BKV + t_lane;
+    const uint32_t t_pv = tmem_base + TM_PV + t * 128 + t_lane;
     const float c = p.scale_log2;
+    const int my_n_kv = n_kv_t[t];
     int limit = p.Skv;                    // keys [0, limit) are visible to this row
     if (p.causal) {
       const int l2 = row + shift + 1;
@@ -229,13 +283,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int i = 0; i < D; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int b = j & 1;
-      ok = mbar_wait(bar_sfull + 8 * b, (j >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_SOFTMAX,
-                     p.spin);
+    for (int j = 0; j < my_n_kv && ok; ++j) {
+      ok = mbar_wait(bar_sfull + 8 * t, j & 1u, abort_flag, p.status, DEV_TIMEOUT_SOFTMAX, p.spin);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t t_s = tmem_base + TM_S + b * BKV + t_lane;
       const int kv0 = j * BKV;
       const bool need_mask = kv0 + BKV > limit;
       // pass 1: row max
@@ -256,66 +307,61 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = ex2_approx((m - m_use) * c);  // m = -inf -> 0
-      // fold in the previous block's P.V while this block's P is still to be written
+      // fold in the previous block's P.V (complete by now: S_t(j) was issued after it)
       if (j > 0) {
-        ok = mbar_wait(bar_pvfull, (j - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
+        ok = mbar_wait(bar_pvfull + 8 * t, (j - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem_base + TM_PV + t_lane + c0, v);
+          tmem_ld_32x32(t_pv + c0, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
         }
-        tc_fence_before();
-        mbar_arrive(bar_pvempty);
       }
-      // pass 2: P = exp2(c*(s - m)) -> bf16 -> shared memory (K-major, 128B swizzle)
+      // pass 2: P = exp2(c*(s - m)) as bf16, written over the first half of the S columns
+      // (keys [c0, c0+64) -> columns [c0/2, c0/2+32); those S columns have been read by then)
       const float mc = m_use * c;
       float rs = 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c0, v);
-        tmem_ld_wait();
-        float e[32];
+      for (int c0 = 0; c0 < BKV; c0 += 64) {
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = ex2_approx(fmaf(__uint_as_float(v[i]), c, -mc));
-          if (need_mask && !(kv0 + c0 + i < limit)) x = 0.f;
-          e[i] = x;
-          rs += x;
-        }
-        uint8_t* prow = gP + (c0 >> 6) * PANEL + r * 128;
-        const int chunk0 = (c0 & 63) >> 3;
+        for (int h = 0; h < 2; ++h) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_s + c0 + 32 * h, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 pk;
-          pk.x = pack_bf16x2(e[8 * ch + 0], e[8 * ch + 1]);
-          pk.y = pack_bf16x2(e[8 * ch + 2], e[8 * ch + 3]);
-          pk.z = pack_bf16x2(e[8 * ch + 4], e[8 * ch + 5]);
-          pk.w = pack_bf16x2(e[8 * ch + 6], e[8 * ch + 7]);
-          *reinterpret_cast<uint4*>(prow + (((chunk0 + ch) ^ (r & 7)) << 4)) = pk;
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = ex2_approx(fmaf(__uint_as_float(v[i]), c, -mc));
+            float x1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), c, -mc));
+            if (need_mask) {
+              if (!(kv0 + c0 + 32 * h + i < limit)) x0 = 0.f;
+              if (!(kv0 + c0 + 32 * h + i + 1 < limit)) x1 = 0.f;
+            }
+            rs += x0 + x1;
+            pk[16 * h + (i >> 1)] = pack_bf16x2(x0, x1);
+          }
         }
+        tmem_st_32x32(t_s + (c0 >> 1), pk);
       }
+      tmem_st_wait();
       l = l * alpha + rs;
       m = mx;
       alpha_prev = alpha;
-      fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(bar_pfull);
-      mbar_arrive(bar_sempty + 8 * b);
+      mbar_arrive(bar_pfull + 8 * t);
     }
-    if (ok && n_kv > 0) {
-      ok = mbar_wait(bar_pvfull, (n_kv - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
+    if (ok && my_n_kv > 0) {
+      ok = mbar_wait(bar_pvfull + 8 * t, (my_n_kv - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem_base + TM_PV + t_lane + c0, v);
+          tmem_ld_32x32(t_pv + c0, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
@@ -375,7 +421,7 @@ kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   auto kern = fmha_fwd_kernel<D>;
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::SMEM_TOTAL));
-  dim3 grid((p.Sq + BQ - 1) / BQ, bh);
+  dim3 grid((p.Sq + QTILES * BQ - 1) / (QTILES * BQ), bh);
   kern<<<grid, FM_THREADS, Cfg::SMEM_TOTAL, stream>>>(tq, tk, tv, p);
   g_launches.fetch_add(1);
   KCG_CUDA_TRY(cudaGetLastError());
