@@ -81,7 +81,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int DPANELS = D / 64;
   constexpr uint32_t IDESC_S = make_idesc(UMMA_FMT_BF16, BQ, BKV, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc(UMMA_FMT_BF16, BQ, D, 0, 1);
-  constexpr uint32_t TM_S = 0, TM_PV = 256;           // + 128 * tile
+  constexpr uint32_t TM_S = 0, TM_O = 256;            // + 128 * tile
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -204,13 +204,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit(bar_sfull + 8 * t);
       };
       auto issue_pv = [&](int t, int j) {
-        // PV_t(j) = P_t(j) . V_j with P_t in the TMEM columns of S_t (16 keys = 8 columns)
+        // O_t (+)= P_t(j) . V_j with P_t in the TMEM columns of S_t (16 keys = 8 columns); the
+        // accumulator stays in TMEM across blocks, the softmax warps rescale it in place when the
+        // row maximum moves
         const uint32_t vb = sV + (j & 1) * TILE;
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks) {
           const uint64_t vd = make_smem_desc(vb + ks * 2048, PANEL, 1024);
-          umma_bf16_ts(tmem_base + TM_PV + t * 128, tmem_base + TM_S + t * BKV + ks * 8, vd, IDESC_PV,
-                       ks ? 1u : 0u);
+          umma_bf16_ts(tmem_base + TM_O + t * 128, tmem_base + TM_S + t * BKV + ks * 8, vd, IDESC_PV,
+                       (j | ks) ? 1u : 0u);
         }
         umma_commit(bar_pvfull + 8 * t);
       };
@@ -270,7 +272,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int row = q0 + t * BQ + r;      // query index
     const uint32_t t_lane = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t t_s = tmem_base + TM_S + t * BKV + t_lane;
-    const uint32_t t_pv = tmem_base + TM_PV + t * 128 + t_lane;
+    const uint32_t t_o = tmem_base + TM_O + t * 128 + t_lane;
     const float c = p.scale_log2;
     const int my_n_kv = n_kv_t[t];
     int limit = p.Skv;                    // keys [0, limit) are visible to this row
@@ -278,10 +280,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int l2 = row + shift + 1;
       limit = l2 < limit ? l2 : limit;
     }
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    // m = the row maximum the exponentials are currently taken against (raw S units).  It is
+    // only raised when the true maximum has grown by more than 2^RESCALE_LOG2 (lazy rescale);
+    // until then P may exceed 1 by at most that factor, harmless in bf16/fp32, and O and l stay
+    // consistent because both are scaled against the same m.
+    constexpr float RESCALE_LOG2 = 8.f;
+    float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_n_kv && ok; ++j) {
       ok = mbar_wait(bar_sfull + 8 * t, j & 1u, abort_flag, p.status, DEV_TIMEOUT_SOFTMAX, p.spin);
@@ -289,71 +293,73 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const int kv0 = j * BKV;
       const bool need_mask = kv0 + BKV > limit;
-      // pass 1: row max
-      float mx = m;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c0, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      // the whole S row of this thread: 128 fp32 in registers
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) tmem_ld_32x32(t_s + 32 * g, sr[g]);
+      tmem_ld_wait();
+      if (need_mask) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (kv0 + c0 + i < limit) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
+            if (!(kv0 + 32 * g + i < limit)) sr[g][i] = 0xFF800000u;  // -inf
       }
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = ex2_approx((m - m_use) * c);  // m = -inf -> 0
-      // fold in the previous block's P.V (complete by now: S_t(j) was issued after it)
-      if (j > 0) {
-        ok = mbar_wait(bar_pvfull + 8 * t, (j - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
-        if (!ok) break;
-        tc_fence_after();
+      float mx = -INFINITY;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_pv + c0, v);
-          tmem_ld_wait();
+      for (int g = 0; g < 4; ++g)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
-        }
-      }
-      // pass 2: P = exp2(c*(s - m)) as bf16, written over the first half of the S columns
-      // (keys [c0, c0+64) -> columns [c0/2, c0/2+32); those S columns have been read by then)
-      const float mc = m_use * c;
-      float rs = 0.f;
+        for (int i = 0; i < 32; i += 2) mx = fmax3(mx, __uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1]));
+      // lazy rescale (warp-uniform decision: the TMEM accesses below are warp-collective)
+      const bool grow = (mx - m) * c > RESCALE_LOG2 || (m == -INFINITY && mx != -INFINITY);
+      if (__any_sync(0xFFFFFFFFu, grow)) {
+        const float m_new = grow ? mx : m;
+        const float alpha = (m == -INFINITY) ? 0.f : ex2_approx((m - m_new) * c);
+        l *= alpha;
+        m = m_new;
+        if (j > 0) {
+          // O_t must be at rest: PV_t(j-1) complete (it is, in steady state: S_t(j) came after it)
+          ok = mbar_wait(bar_pvfull + 8 * t, (j - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 64) {
-        uint32_t pk[32];
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_o + c0, v);
+            tmem_ld_wait();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_s + c0 + 32 * h, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = ex2_approx(fmaf(__uint_as_float(v[i]), c, -mc));
-            float x1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), c, -mc));
-            if (need_mask) {
-              if (!(kv0 + c0 + 32 * h + i < limit)) x0 = 0.f;
-              if (!(kv0 + c0 + 32 * h + i + 1 < limit)) x1 = 0.f;
-            }
-            rs += x0 + x1;
-            pk[16 * h + (i >> 1)] = pack_bf16x2(x0, x1);
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(t_o + c0, v);
           }
         }
-        tmem_st_32x32(t_s + (c0 >> 1), pk);
+      }
+      // P = exp2(c*s - c*m) as bf16, written over the first 64 columns of this S buffer
+      const float mc = (m == -INFINITY) ? 0.f : m * c;
+      float2 rs2 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float2 x = fma2(make_float2(__uint_as_float(sr[2 * hh + g][i]), __uint_as_float(sr[2 * hh + g][i + 1])),
+                            make_float2(c, c), make_float2(-mc, -mc));
+            x.x = ex2_approx(x.x);
+            x.y = ex2_approx(x.y);
+            rs2 = add2(rs2, x);
+            pk[16 * g + (i >> 1)] = pack_bf16x2(x.x, x.y);
+          }
+        tmem_st_32x32(t_s + 32 * hh, pk);
       }
       tmem_st_wait();
-      l = l * alpha + rs;
-      m = mx;
-      alpha_prev = alpha;
+      l += rs2.x + rs2.y;
       tc_fence_before();
       mbar_arrive(bar_pfull + 8 * t);
     }
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
     if (ok && my_n_kv > 0) {
       ok = mbar_wait(bar_pvfull + 8 * t, (my_n_kv - 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_PV, p.spin);
       if (ok) {
@@ -361,10 +367,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(t_pv + c0, v);
+          tmem_ld_32x32(t_o + c0, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_prev, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; ++i) o[c0 + i] = __uint_as_float(v[i]);
         }
         tc_fence_before();
       }
