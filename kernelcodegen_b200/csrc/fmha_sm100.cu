@@ -35,6 +35,9 @@ namespace kcg {
 
 namespace {
 
+#ifndef KCG_FMHA_POLY_PER_8
+#define KCG_FMHA_POLY_PER_8 0
+#endif
 constexpr int FM_THREADS = 384;
 constexpr int BQ = 128;        // query rows per tile
 constexpr int QTILES = 2;      // tiles per CTA
@@ -61,14 +64,14 @@ struct FmhaCfg {
 
 // Register re-balancing.  The CTA is launched with 384 threads x 168 registers = 64512; the
 // pool never grows, so after the change the three warpgroups must still fit in 64512:
-// 128 x 40 + 256 x 232 = 64512 exactly.  (setmaxnreg.inc waits, unbounded, for registers to be
+// 128 x 56 + 256 x 224 = 64512 exactly.  (setmaxnreg.inc waits, unbounded, for registers to be
 // released -- a budget that does not add up hangs the CTA.)
-static_assert(128 * 40 + 256 * 232 <= 384 * 168, "setmaxnreg budget must fit the launch allocation");
-__device__ __forceinline__ void reg_dealloc_40() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+static_assert(128 * 56 + 256 * 224 <= 384 * 168, "setmaxnreg budget must fit the launch allocation");
+__device__ __forceinline__ void reg_dealloc_56() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
 }
-__device__ __forceinline__ void reg_alloc_232() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
+__device__ __forceinline__ void reg_alloc_224() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
 }
 
 template <int D>
@@ -151,7 +154,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-    reg_dealloc_40();
+    reg_dealloc_56();
     if (warp == 0 && lane == 0 && n_kv > 0) {
       // ------------------------------- TMA producer -----------------------------------------
 #pragma unroll
@@ -188,48 +191,65 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               break;
           }
       }
-    } else if (warp == 1 && lane == 0 && n_kv > 0) {
+    } else if (warp == 1 && n_kv > 0) {
       // ------------------------------- UMMA issuer -------------------------------------------
+      // all 32 lanes walk the loop and wait on the barriers; one elected lane issues
       bool ok = true;
+      auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+        return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, p.status, code, p.spin));
+      };
+      // The issuing thread has ~64 tensor-core clocks per UMMA to stay ahead of the pipe, so the
+      // descriptors are built once; per instruction only the 16-byte-unit start address (low 14
+      // bits of the descriptor, never overflowing: shared memory is < 256 KB) is advanced.
+      const uint64_t q_desc0 = make_smem_desc(sQ, 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc(sK, 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc(sV, PANEL, 1024);
+      constexpr uint64_t TILE16 = TILE >> 4;
       auto issue_s = [&](int t, int j) {
         // S_t(j) = Q_t . K_j^T; the caller has waited for K_j and for the S_t buffer
-        const uint32_t kb = sK + (j & 1) * TILE;
-        const uint32_t qb = sQ + t * TILE;
+        const uint64_t qd = q_desc0 + t * TILE16, kd = k_desc0 + (j & 1) * TILE16;
+        const uint32_t d_tmem = tmem_base + TM_S + t * BKV;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * PANEL + (ks & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S + t * BKV, make_smem_desc(qb + off, 16, 1024),
-                       make_smem_desc(kb + off, 16, 1024), IDESC_S, ks ? 1u : 0u);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint64_t off = static_cast<uint64_t>(((ks >> 2) * PANEL + (ks & 3) * 32) >> 4);
+            umma_bf16_ss(d_tmem, qd + off, kd + off, IDESC_S, ks ? 1u : 0u);
+          }
+          umma_commit(bar_sfull + 8 * t);
         }
-        umma_commit(bar_sfull + 8 * t);
+        __syncwarp();
       };
       auto issue_pv = [&](int t, int j) {
         // O_t (+)= P_t(j) . V_j with P_t in the TMEM columns of S_t (16 keys = 8 columns); the
         // accumulator stays in TMEM across blocks, the softmax warps rescale it in place when the
-        // row maximum moves
-        const uint32_t vb = sV + (j & 1) * TILE;
+        // row maximum moves.  V tile: D/64 groups of [128 keys x 128 bytes]; 16 keys = 2048 bytes.
+        const uint64_t vd = v_desc0 + (j & 1) * TILE16;
+        const uint32_t d_tmem = tmem_base + TM_O + t * 128;
+        const uint32_t a_tmem = tmem_base + TM_S + t * BKV;
+        if (elect_one()) {
+          umma_bf16_ts(d_tmem, a_tmem, vd, IDESC_PV, j ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < BKV / 16; ++ks) {
-          const uint64_t vd = make_smem_desc(vb + ks * 2048, PANEL, 1024);
-          umma_bf16_ts(tmem_base + TM_O + t * 128, tmem_base + TM_S + t * BKV + ks * 8, vd, IDESC_PV,
-                       (j | ks) ? 1u : 0u);
+          for (int ks = 1; ks < BKV / 16; ++ks)
+            umma_bf16_ts(d_tmem, a_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), IDESC_PV, 1u);
+          umma_commit(bar_pvfull + 8 * t);
         }
-        umma_commit(bar_pvfull + 8 * t);
+        __syncwarp();
       };
       // prologue: S_0(0), S_1(0)
 #pragma unroll
       for (int t = 0; t < QTILES && ok; ++t) {
         if (n_kv_t[t] == 0) continue;
-        ok = mbar_wait(bar_q + 8 * t, 0, abort_flag, p.status, DEV_TIMEOUT_Q, p.spin);
+        ok = wait_all(bar_q + 8 * t, 0, DEV_TIMEOUT_Q);
         if (ok && t == 0)
-          ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin);
+          ok = wait_all(bar_kfull, 0, DEV_TIMEOUT_MMA_FULL);
         if (ok && t == 1 && n_kv_t[0] == 0)
-          ok = mbar_wait(bar_kfull, 0, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin);
+          ok = wait_all(bar_kfull, 0, DEV_TIMEOUT_MMA_FULL);
         if (!ok) break;
         tc_fence_after();
         issue_s(t, 0);
       }
-      if (ok) umma_commit(bar_kempty);  // K_0 is free once S_0(0), S_1(0) have read it
+      if (ok && elect_one()) umma_commit(bar_kempty);  // K_0 is free once S_0(0), S_1(0) have read it
+      __syncwarp();
       for (int j = 0; j < n_kv && ok; ++j) {
         const int b = j & 1;
         const uint32_t par = (j >> 1) & 1u;
@@ -239,18 +259,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int t = 0; t < QTILES && ok; ++t) {
           if (j < n_kv_t[t]) {
             if (t == 0 || j >= n_kv_t[0]) {
-              ok = mbar_wait(bar_vfull + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL, p.spin);
+              ok = wait_all(bar_vfull + 8 * b, par, DEV_TIMEOUT_MMA_FULL);
               if (!ok) break;
             }
-            ok = mbar_wait(bar_pfull + 8 * t, j & 1u, abort_flag, p.status, DEV_TIMEOUT_P, p.spin);
+            ok = wait_all(bar_pfull + 8 * t, j & 1u, DEV_TIMEOUT_P);
             if (!ok) break;
             tc_fence_after();
             issue_pv(t, j);
           }
           if (next && j + 1 < n_kv_t[t]) {
             if (!k_next_ready) {
-              ok = mbar_wait(bar_kfull + 8 * (b ^ 1), ((j + 1) >> 1) & 1u, abort_flag, p.status,
-                             DEV_TIMEOUT_MMA_FULL, p.spin);
+              ok = wait_all(bar_kfull + 8 * (b ^ 1), ((j + 1) >> 1) & 1u, DEV_TIMEOUT_MMA_FULL);
               if (!ok) break;
               k_next_ready = true;
               tc_fence_after();
@@ -259,13 +278,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
         if (!ok) break;
-        umma_commit(bar_vempty + 8 * b);
-        if (next) umma_commit(bar_kempty + 8 * (b ^ 1));
+        if (elect_one()) {
+          umma_commit(bar_vempty + 8 * b);
+          if (next) umma_commit(bar_kempty + 8 * (b ^ 1));
+        }
+        __syncwarp();
       }
     }
   } else {
     // ------------------------------- softmax / output (2 x 4 warps) --------------------------
-    reg_alloc_232();
+    reg_alloc_224();
     const int t = (warp >> 2) - 1;        // tile of this warpgroup
     const int q = warp & 3;               // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;          // row inside the tile == TMEM lane
@@ -285,6 +307,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // until then P may exceed 1 by at most that factor, harmless in bf16/fp32, and O and l stay
     // consistent because both are scaled against the same m.
     constexpr float RESCALE_LOG2 = 8.f;
+    constexpr int POLY_PER_8 = KCG_FMHA_POLY_PER_8;   // pairs out of every 8 whose exp2 runs on the FMA pipe
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_n_kv && ok; ++j) {
@@ -305,11 +328,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; ++i)
             if (!(kv0 + 32 * g + i < limit)) sr[g][i] = 0xFF800000u;  // -inf
       }
-      float mx = -INFINITY;
+      // four independent chains keep the max reduction off the critical path
+      float mxg[4];
 #pragma unroll
-      for (int g = 0; g < 4; ++g)
+      for (int g = 0; g < 4; ++g) {
+        mxg[g] = fmax3(__uint_as_float(sr[g][0]), __uint_as_float(sr[g][1]), __uint_as_float(sr[g][2]));
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) mx = fmax3(mx, __uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1]));
+        for (int i = 3; i < 31; i += 2) mxg[g] = fmax3(mxg[g], __uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1]));
+        mxg[g] = fmaxf(mxg[g], __uint_as_float(sr[g][31]));
+      }
+      const float mx = fmaxf(fmaxf(mxg[0], mxg[1]), fmaxf(mxg[2], mxg[3]));
       // lazy rescale (warp-uniform decision: the TMEM accesses below are warp-collective)
       const bool grow = (mx - m) * c > RESCALE_LOG2 || (m == -INFINITY && mx != -INFINITY);
       if (__any_sync(0xFFFFFFFFu, grow)) {
@@ -335,7 +363,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // P = exp2(c*s - c*m) as bf16, written over the first 64 columns of this S buffer
       const float mc = (m == -INFINITY) ? 0.f : m * c;
-      float2 rs2 = make_float2(0.f, 0.f);
+      // The MUFU unit (16 exp2 per clock per SM) needs as long for a 128x128 block as the
+      // tensor core needs for its two contractions, so a share of the exponentials
+      // (POLY_PER_8 of every 8 pairs) is evaluated on the FMA pipe instead: Cody-Waite range
+      // reduction + cubic minimax polynomial, relative error ~1e-4 (P is rounded to bf16 anyway).
+      float2 rsg[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) rsg[g] = make_float2(0.f, 0.f);
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t pk[32];
@@ -345,13 +379,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; i += 2) {
             float2 x = fma2(make_float2(__uint_as_float(sr[2 * hh + g][i]), __uint_as_float(sr[2 * hh + g][i + 1])),
                             make_float2(c, c), make_float2(-mc, -mc));
-            x.x = ex2_approx(x.x);
-            x.y = ex2_approx(x.y);
-            rs2 = add2(rs2, x);
+            if (((i >> 1) & 7) < POLY_PER_8) {
+              x = exp2_poly2(x);
+            } else {
+              x.x = ex2_approx(x.x);
+              x.y = ex2_approx(x.y);
+            }
+            rsg[(i >> 1) & 3] = add2(rsg[(i >> 1) & 3], x);
             pk[16 * g + (i >> 1)] = pack_bf16x2(x.x, x.y);
           }
         tmem_st_32x32(t_s + 32 * hh, pk);
       }
+      const float2 rs2 = add2(add2(rsg[0], rsg[1]), add2(rsg[2], rsg[3]));
       tmem_st_wait();
       l += rs2.x + rs2.y;
       tc_fence_before();

@@ -31,6 +31,22 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp.  The UMMA / TMA issue paths run with the whole warp in uniform
+// control flow and only the issuing instruction under this predicate: descriptors and
+// addresses then stay warp-uniform values (uniform registers), which is what the tensor-core
+// and TMA instructions consume; issuing from inside a divergent `lane == 0` region costs a
+// register-to-uniform transfer per operand and limits the issue rate to roughly one UMMA per
+// 85 clocks.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- mbarrier ------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -257,6 +273,25 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   float2 d;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(pd));
   return d;
+}
+
+// 2^x for a pair of values on the FMA/ALU pipes (no MUFU): x is clamped to >= -126, split into
+// n = round(x) and f = x - n in [-0.5, 0.5] with the 1.5*2^23 trick, 2^f by a cubic minimax
+// polynomial (max relative error 7.6e-5 on [-0.5, 0.5]), and n added into the exponent field.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float MAGIC = 12582912.f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = add2(x, make_float2(MAGIC, MAGIC));
+  const float2 n = add2(t, make_float2(-MAGIC, -MAGIC));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+  float2 pz = fma2(f, make_float2(0.0552055053f, 0.0552055053f), make_float2(0.2426139712f, 0.2426139712f));
+  pz = fma2(pz, f, make_float2(0.6932547688f, 0.6932547688f));
+  pz = fma2(pz, f, make_float2(0.9999276996f, 0.9999276996f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(pz.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(pz.y) + (__float_as_int(t.y) << 23));
+  return r;
 }
 
 }  // namespace kcg
