@@ -194,57 +194,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     // ------------------------------- UMMA issuer ---------------------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop and waits on the barriers; one elected lane issues, so
+    // descriptors and addresses stay warp-uniform (see elect_one()).
+    {
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      const uint64_t a_desc0 = make_smem_desc(base, 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc(base + Cfg::NOPS * A_BYTES, B_LBO, B_SBO, B_LAYOUT);
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status,
-                       DEV_TIMEOUT_MMA_TMEM, p.spin);
+        ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status,
+                                               DEV_TIMEOUT_MMA_TMEM, p.spin));
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL,
-                         p.spin);
+          ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status,
+                                                 DEV_TIMEOUT_MMA_FULL, p.spin));
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sA = base + stage * STAGE_BYTES;
-          const uint32_t sB = sA + Cfg::NOPS * A_BYTES;
-          if (KIND == 2) {
-            // small terms first: a_lo*b_hi, a_hi*b_lo, then a_hi*b_hi
+          // start-address field (16-byte units) of this stage's operand tiles
+          const uint64_t ad0 = a_desc0 + static_cast<uint64_t>((stage * STAGE_BYTES) >> 4);
+          const uint64_t bd0 = b_desc0 + static_cast<uint64_t>((stage * STAGE_BYTES) >> 4);
+          if (elect_one()) {
+            if (KIND == 2) {
+              // small terms first: a_lo*b_hi, a_hi*b_lo, then a_hi*b_hi
 #pragma unroll
-            for (int pass = 0; pass < 3; ++pass) {
-              const uint32_t a_off = (pass == 0) ? A_BYTES : 0;
-              const uint32_t b_off = (pass == 1) ? B_BYTES : 0;
+              for (int pass = 0; pass < 3; ++pass) {
+                const uint64_t a_off = (pass == 0) ? (A_BYTES >> 4) : 0;
+                const uint64_t b_off = (pass == 1) ? (B_BYTES >> 4) : 0;
+#pragma unroll
+                for (int k = 0; k < BK / UK; ++k)
+                  umma_tf32_ss(d_tmem, ad0 + a_off + ((k * 32) >> 4), bd0 + b_off + ((k * B_KSTEP) >> 4), IDESC,
+                               (kb | pass | k) ? 1u : 0u);
+              }
+            } else {
 #pragma unroll
               for (int k = 0; k < BK / UK; ++k) {
-                const uint64_t ad = make_smem_desc(sA + a_off + k * 32, 16, 1024);
-                const uint64_t bd = make_smem_desc(sB + b_off + k * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-                umma_tf32_ss(d_tmem, ad, bd, IDESC, (kb | pass | k) ? 1u : 0u);
+                const uint64_t ad = ad0 + ((k * 32) >> 4);
+                const uint64_t bd = bd0 + ((k * B_KSTEP) >> 4);
+                if (KIND == 0)
+                  umma_bf16_ss(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
+                else
+                  umma_tf32_ss(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
               }
             }
-          } else {
-#pragma unroll
-            for (int k = 0; k < BK / UK; ++k) {
-              const uint64_t ad = make_smem_desc(sA + k * 32, 16, 1024);
-              const uint64_t bd = make_smem_desc(sB + k * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-              if (KIND == 0)
-                umma_bf16_ss(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
-              else
-                umma_tf32_ss(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
-            }
+            umma_commit(bar_empty + 8 * stage);  // stage reusable once these UMMAs have read it
           }
-          umma_commit(bar_empty + 8 * stage);  // stage reusable once these UMMAs have read it
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(bar_tfull + 8 * acc);
+        if (ok) {
+          if (elect_one()) umma_commit(bar_tfull + 8 * acc);
+          __syncwarp();
+        }
       }
     }
   } else {
