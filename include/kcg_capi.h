@@ -104,7 +104,8 @@ typedef struct kcg_fmha_desc {
   int32_t reserved;
 } kcg_fmha_desc;
 
-/* Scratch the launch needs (bytes; may be 0). 3xTF32 GEMM: hi/lo split copies of A and B.
+/* Scratch the launch needs (bytes; may be 0). 3xTF32 GEMM: the fp32 residuals (x minus its
+ * TF32 truncation) of A and B, 4*(M*K + K*N) bytes, each array rounded up to 256.
  * FMHA with f32 inputs: bf16 copies of Q, K, V. */
 size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d);
 size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d);
@@ -118,13 +119,14 @@ kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* 
  * over a workspace because they cannot allocate device memory at all: a plug-in running inside
  * a host whose allocator has reserved the whole GPU up front (a cudaMalloc there fails or
  * fragments the host's pool), or a latency-critical loop where an allocation's implicit
- * device synchronisation is not acceptable.  The hi/lo split copies of A and B go into a
+ * device synchronisation is not acceptable.  The TF32 residuals of A and B go into a
  * fixed array that is part of the library image, KCG_STATIC_SCRATCH_BYTES (32 MiB) on every
  * GPU that loads the library, held until the process exits.  This call performs no
  * cudaMalloc/cudaFree and calls nothing that allocates.
  *   - Limit: kcg_gemm_workspace_bytes(d) <= KCG_STATIC_SCRATCH_BYTES, i.e.
- *     8*(M*K + K*N) bytes (each term rounded up to 256) -- e.g. up to 1024 x N x 1024 with
- *     N <= 3072.  Larger problems return KCG_TOO_LARGE (and say so on stderr).
+ *     4*(M*K + K*N) bytes (each term rounded up to 256) -- e.g. up to 1024 x N x 1024 with
+ *     N <= 7168, or 2048 x 2048 x 2048.  Larger problems return KCG_TOO_LARGE (and say so on
+ *     stderr).
  *   - Only precision KCG_PREC_3XTF32 (the one path that needs scratch); others:
  *     KCG_UNSUPPORTED -- use kcg_gemm_launch with a NULL workspace for those.
  *   - The first call on each device looks up the array's device address; make that first

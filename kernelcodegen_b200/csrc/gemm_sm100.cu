@@ -360,29 +360,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
-// fp32 -> (hi, lo) with hi = x with the 13 low mantissa bits cleared (exactly representable in
-// TF32, so the tensor core sees it unchanged whatever its input rounding) and lo = x - hi
-// (exact in fp32).  Output is compact [rows, cols].
-__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi,
-                                  float* __restrict__ lo, long long rows, int cols4,
-                                  long long ld) {
-  const long long total = rows * cols4;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+// Residuals for the 3xTF32 product: lo = x - hi with hi = x with the 13 low mantissa bits cleared
+// (exact in fp32).  The tensor core itself truncates fp32 operands to TF32 (measured: 1 + 2^-11 +
+// 2^-12 multiplies as 1.0), so the original arrays serve as the hi operands and only the
+// residuals are materialised.  One launch covers both operands; outputs are compact [rows, cols].
+struct SplitArgs {
+  const float* src;
+  float* lo;
+  long long rows;
+  int cols4;
+  long long ld;
+};
+__global__ void split_lo_kernel(SplitArgs a, SplitArgs b) {
+  const long long na = a.rows * a.cols4, nb = b.rows * b.cols4;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < na + nb;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / cols4;
-    const int c = static_cast<int>(i - r * cols4);
-    const float4 v = *reinterpret_cast<const float4*>(src + r * ld + 4ll * c);
-    float4 h, l;
-    h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-    h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-    h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-    h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-    l.x = v.x - h.x;
-    l.y = v.y - h.y;
-    l.z = v.z - h.z;
-    l.w = v.w - h.w;
-    reinterpret_cast<float4*>(hi)[i] = h;
-    reinterpret_cast<float4*>(lo)[i] = l;
+    const bool second = i >= na;
+    const SplitArgs& s = second ? b : a;
+    const long long k = second ? i - na : i;
+    const long long r = k / s.cols4;
+    const int c = static_cast<int>(k - r * s.cols4);
+    const float4 v = *reinterpret_cast<const float4*>(s.src + r * s.ld + 4ll * c);
+    float4 l;
+    l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+    l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+    l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+    l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+    reinterpret_cast<float4*>(s.lo)[k] = l;
   }
 }
 
@@ -431,7 +435,7 @@ size_t gemm_workspace_impl(const kcg_gemm_desc* d) {
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
   const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
   const size_t b = pad256(static_cast<size_t>(d->K) * d->N * 4);
-  return 2 * a + 2 * b;
+  return a + b;
 }
 
 kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
@@ -470,31 +474,26 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   const void* pa2 = A;
   const void* pb2 = B;
   long long lda = d->lda, ldb = d->ldb;
+  long long lda2 = d->lda, ldb2 = d->ldb;  // leading dimensions of the residual arrays
   if (kind == 2) {
     const size_t need = gemm_workspace_impl(d);
     if (!ws || ws_bytes < need || !aligned16(ws)) return KCG_BAD_WORKSPACE;
     if ((d->K % 4) || (d->N % 4)) return KCG_BAD_ALIGN;
     const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
-    const size_t b = pad256(static_cast<size_t>(d->K) * d->N * 4);
-    float* a_hi = static_cast<float*>(ws);
-    float* a_lo = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + a);
-    float* b_hi = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + 2 * a);
-    float* b_lo = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + 2 * a + b);
+    float* a_lo = static_cast<float*>(ws);
+    float* b_lo = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + a);
     const int sms = device_sm_count();
     const long long b_rows = b_kmajor ? d->N : d->K;
     const long long b_cols = b_kmajor ? d->K : d->N;
-    split_tf32_kernel<<<sms * 4, 256, 0, stream>>>(static_cast<const float*>(A), a_hi, a_lo, d->M,
-                                                    static_cast<int>(d->K / 4), d->lda);
-    split_tf32_kernel<<<sms * 4, 256, 0, stream>>>(static_cast<const float*>(B), b_hi, b_lo,
-                                                    b_rows, static_cast<int>(b_cols / 4), d->ldb);
-    g_launches.fetch_add(2);
+    SplitArgs sa{static_cast<const float*>(A), a_lo, d->M, static_cast<int>(d->K / 4), d->lda};
+    SplitArgs sb{static_cast<const float*>(B), b_lo, b_rows, static_cast<int>(b_cols / 4), d->ldb};
+    split_lo_kernel<<<sms * 4, 256, 0, stream>>>(sa, sb);
+    g_launches.fetch_add(1);
     KCG_CUDA_TRY(cudaGetLastError());
-    pa = a_hi;
     pa2 = a_lo;
-    pb = b_hi;
     pb2 = b_lo;
-    lda = d->K;
-    ldb = b_cols;
+    lda2 = d->K;
+    ldb2 = b_cols;
   }
 
   using Cfg0 = GemmCfg<0, 128>;
@@ -506,10 +505,11 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(lda) * es};
+    const uint64_t strides2[1] = {static_cast<uint64_t>(lda2) * es};
     const uint32_t box[2] = {bk, BM};
     kcg_status_t st = encode_tmap(&tA, dt, 2, pa, dims, strides, box);
     if (st != KCG_OK) return st;
-    st = encode_tmap(&tA2, dt, 2, pa2, dims, strides, box);
+    st = encode_tmap(&tA2, dt, 2, pa2, dims, strides2, box);
     if (st != KCG_OK) return st;
   }
   {
@@ -529,9 +529,10 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
     const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * es};
     const CUtensorMapSwizzle sw = (!b_kmajor && es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                          : CU_TENSOR_MAP_SWIZZLE_128B;
+    const uint64_t strides2[1] = {static_cast<uint64_t>(ldb2) * es};
     kcg_status_t st = encode_tmap(&tB, dt, 2, pb, dims, strides, box, sw);
     if (st != KCG_OK) return st;
-    st = encode_tmap(&tB2, dt, 2, pb2, dims, strides, box, sw);
+    st = encode_tmap(&tB2, dt, 2, pb2, dims, strides2, box, sw);
     if (st != KCG_OK) return st;
   }
 

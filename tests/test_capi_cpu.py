@@ -48,7 +48,7 @@ def _gemm_desc(m=256, n=256, k=256, prec=capi.KCG_PREC_3XTF32, dt=capi.KCG_F32):
 
 def test_workspace_sizes(native_lib):
     d = _gemm_desc()
-    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 4 * 256 * 256 * 4
+    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 256 * 4
     d = _gemm_desc(prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)
     assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 0
     f = capi.FmhaDesc()

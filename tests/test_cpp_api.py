@@ -104,7 +104,7 @@ def test_optimize_fuses_relu_and_dispatches(stages):
     code = stages["codegen_matmul_relu"]
     assert "namespace matmul_demo" in code and "kernel0(const float* A, const float* B, float* C" in code
     assert "d.M = 4096; d.N = 2048; d.K = 1024;" in code and "d.epilogue = 1;" in code and "d.precision = 0;" in code
-    assert "plans 1 status 0 epilogue 1 buffers 012 ws 50331648" in code
+    assert "plans 1 status 0 epilogue 1 buffers 012 ws 25165824" in code
 
 
 def test_fmha_chain_is_fused(stages):

@@ -62,7 +62,7 @@ def test_static_scratch_entry_refuses_what_does_not_fit(cuda_device):
     from kernelcodegen_b200 import capi
 
     lib = capi.load()
-    m = n = k = 2048  # needs 8 * (m*k + k*n) = 64 MiB of scratch, the array holds 32 MiB
+    m, n, k = 4096, 2048, 2048  # needs 4 * (m*k + k*n) = 48 MiB of scratch, the array holds 32 MiB
     d = _desc(capi, m, n, k)
     assert lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) > capi.KCG_STATIC_SCRATCH_BYTES
     a = torch.zeros((m, k), device=cuda_device)
