@@ -35,8 +35,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the bf16 GEMM kernel, from the
 # ncu capture summarised in profiles/ (8192^3 case) scaled to 32768^3 by tiles processed.
-# (profiles/gemm_bf16_8192_ncu.md: 1.023 GB read + 0.139 GB written.)
-GEMM_BF16_DRAM_BYTES_PER_LAUNCH_8192 = 1.163e9
+# (profiles/gemm_bf16_8192_ncu.md: 1.011 GB read + 0.130 GB written.)
+GEMM_BF16_DRAM_BYTES_PER_LAUNCH_8192 = 1.141e9
 
 
 def load_peaks():
