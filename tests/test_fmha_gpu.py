@@ -166,3 +166,25 @@ def test_error_statuses(cuda_device):
     with pytest.raises(capi.KcgError) as ei:
         ops.fmha(z, z, z, scale=-1.0)
     assert ei.value.status == capi.KCG_BAD_ARGUMENT
+
+
+@pytest.mark.parametrize("growth", [0.05, 0.6, 3.0])
+def test_row_maximum_that_keeps_growing(cuda_device, growth):
+    """Logits that increase along the key axis make the running row maximum move in every key
+    block: slowly (below the lazy-rescale threshold, so O is never rescaled), moderately, and
+    fast (rescale in every block).  All three must agree with the oracle."""
+    from kernelcodegen_b200 import ops
+
+    b, h, s, d = 1, 2, 1024, 64
+    q = torch.ones((b, h, s, d)) * 0.25 + normal((b, h, s, d), 11) * 0.05
+    ramp = torch.linspace(0.0, growth * (s / 128), s)[None, None, :, None]        # per-key offset
+    k = normal((b, h, s, d), 12) * 0.05 + ramp / (0.25 * d)                         # q.k grows by `growth` per block
+    v = normal((b, h, s, d), 13)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    for causal in (False, True):
+        want = oracle.fmha(q.float().numpy(), k.float().numpy(), v.float().numpy(), scale=1.0, causal=causal, threads=0)
+        got = ops.fmha(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), scale=1.0, causal=causal,
+                       out_dtype=torch.float32)
+        assert torch.isfinite(got).all()
+        assert rel_err(got.cpu().numpy(), want) <= BF16_TOL
+    assert ops.last_device_status() == 0
