@@ -41,6 +41,10 @@ std::string CUDAGen(mlir::ModuleOp& module);
 // Bytes of scratch the module's launches need (maximum over launches).
 size_t workspaceBytes(mlir::ModuleOp& module);
 
+// Sum of the measured device times (ms) of the module's launches, on scratch buffers; negative
+// when nothing could be measured (no device, or an unsupported launch).
+float timeModule(mlir::ModuleOp& module, int iters = 10);
+
 // Runs every launch of the module on `stream`.  `buffers[i]` is the device pointer of the i-th
 // module-level memref.alloc (PlaceHolders and operator outputs, in creation order); entries of
 // buffers no kernel touches may be null.

@@ -87,8 +87,15 @@ class KernelCodeGenerator {
   mlir::ModuleOp& optimize(ComputeDAG& graph_);
 
   // Cost of a scheduled module; lower is better.  A stub returning 0 in the reference
-  // (include/KernelCodeGen.h:119-121) and here: the first applicable configuration wins.
-  float evaluate(mlir::ModuleOp&) { return 0.0f; }
+  // (include/KernelCodeGen.h:119-121).  Here: the measured device time (ms) of the module's
+  // launches when a GPU is present, so that several knob configurations really compete; 0 when
+  // nothing can be measured (no device), in which case the first applicable configuration wins
+  // as in the reference.
+  float evaluate(mlir::ModuleOp& module) {
+    if (platform != "CUDA") return 0.0f;
+    const float ms = timeModule(module);
+    return ms > 0.f ? ms : 0.0f;
+  }
 
   // Launcher source for the module (see include/Backend/CUDA.h).
   std::string codegen(mlir::ModuleOp module) {

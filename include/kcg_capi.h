@@ -153,6 +153,12 @@ kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* h
 kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const void* hK,
                                const void* hV, void* hO);
 
+/* Average device time of one launch (ms) on zero-filled scratch buffers the call allocates and
+ * frees itself: the cost function behind KernelCodeGenerator::evaluate (a stub returning 0 in
+ * the reference, include/KernelCodeGen.h:119-121).  KCG_CUDA_ERROR when no device is present. */
+kcg_status_t kcg_gemm_time(const kcg_gemm_desc* d, int iters, float* ms_per_launch);
+kcg_status_t kcg_fmha_time(const kcg_fmha_desc* d, int iters, float* ms_per_launch);
+
 /* Buffers other ranks' kernels can store into (one process per GPU, same node).  The fused
  * all-gather of C needs every rank's C buffer mapped into every other rank:
  *   kcg_peer_alloc  allocates `bytes` of device memory and returns a 64-byte handle that can

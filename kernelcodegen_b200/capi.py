@@ -39,6 +39,8 @@ EXPORTED_SYMBOLS = (
     "kcg_fmha_fwd_launch",
     "kcg_gemm_host",
     "kcg_fmha_fwd_host",
+    "kcg_gemm_time",
+    "kcg_fmha_time",
     "kcg_peer_alloc",
     "kcg_peer_open",
     "kcg_peer_close",
@@ -109,6 +111,10 @@ def load() -> ctypes.CDLL:
     lib.kcg_gemm_host.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p]
     lib.kcg_fmha_fwd_host.restype = c_int
     lib.kcg_fmha_fwd_host.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.kcg_gemm_time.restype = c_int
+    lib.kcg_gemm_time.argtypes = [POINTER(GemmDesc), c_int, POINTER(c_float)]
+    lib.kcg_fmha_time.restype = c_int
+    lib.kcg_fmha_time.argtypes = [POINTER(FmhaDesc), c_int, POINTER(c_float)]
     lib.kcg_peer_alloc.restype = c_int
     lib.kcg_peer_alloc.argtypes = [c_size_t, POINTER(c_void_p), c_void_p]
     lib.kcg_peer_open.restype = c_int

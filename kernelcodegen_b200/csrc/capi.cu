@@ -1,6 +1,7 @@
 // extern "C" surface of the library (declared in include/kcg_capi.h) plus the host-side
 // plumbing the launchers share.
 #include <cstring>
+#include <functional>
 #include <mutex>
 
 #include "common.cuh"
@@ -240,6 +241,68 @@ kcg_status_t kcg_peer_free(void* ptr) {
   if (!ptr) return KCG_BAD_ARGUMENT;
   KCG_CUDA_TRY(cudaFree(ptr));
   return KCG_OK;
+}
+
+// ---- timing helpers (the cost function of the operator API's configuration search) -------------
+static kcg_status_t time_launches(const std::function<kcg_status_t()>& launch, int iters, float* ms) {
+  cudaEvent_t e0, e1;
+  KCG_CUDA_TRY(cudaEventCreate(&e0));
+  KCG_CUDA_TRY(cudaEventCreate(&e1));
+  kcg_status_t st = KCG_OK;
+  for (int i = 0; i < 2 && st == KCG_OK; ++i) st = launch();
+  if (st == KCG_OK) {
+    cudaEventRecord(e0, nullptr);
+    for (int i = 0; i < iters && st == KCG_OK; ++i) st = launch();
+    cudaEventRecord(e1, nullptr);
+    if (cudaEventSynchronize(e1) != cudaSuccess) st = KCG_CUDA_ERROR;
+    float t = 0.f;
+    if (st == KCG_OK && cudaEventElapsedTime(&t, e0, e1) == cudaSuccess) *ms = t / iters;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (st == KCG_OK && kcg_last_device_status() != 0) st = KCG_DEVICE_TIMEOUT;
+  return st;
+}
+
+kcg_status_t kcg_gemm_time(const kcg_gemm_desc* d, int iters, float* ms_per_launch) {
+  if (!d || !ms_per_launch || iters <= 0) return KCG_BAD_ARGUMENT;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
+  if (d->n_peers != 0) return KCG_UNSUPPORTED;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return KCG_CUDA_ERROR;
+  const size_t es = d->dtype_in == KCG_BF16 ? 2 : 4, os = d->dtype_out == KCG_BF16 ? 2 : 4;
+  const bool bk = d->b_layout == KCG_COL_MAJOR;
+  const size_t ws_bytes = gemm_workspace_impl(d);
+  DevBuf a, b, c, ws;
+  KCG_CUDA_TRY(a.alloc(static_cast<size_t>(d->M) * d->lda * es));
+  KCG_CUDA_TRY(b.alloc(static_cast<size_t>(bk ? d->N : d->K) * d->ldb * es));
+  KCG_CUDA_TRY(c.alloc(static_cast<size_t>(d->M) * d->ldc * os));
+  KCG_CUDA_TRY(ws.alloc(ws_bytes));
+  KCG_CUDA_TRY(cudaMemset(a.p, 0, static_cast<size_t>(d->M) * d->lda * es));
+  KCG_CUDA_TRY(cudaMemset(b.p, 0, static_cast<size_t>(bk ? d->N : d->K) * d->ldb * es));
+  return time_launches([&] { return gemm_launch_impl(d, a.p, b.p, c.p, ws.p, ws_bytes, nullptr); }, iters,
+                       ms_per_launch);
+}
+
+kcg_status_t kcg_fmha_time(const kcg_fmha_desc* d, int iters, float* ms_per_launch) {
+  if (!d || !ms_per_launch || iters <= 0) return KCG_BAD_ARGUMENT;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0 || d->D <= 0) return KCG_BAD_SHAPE;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return KCG_CUDA_ERROR;
+  const size_t es = d->dtype_in == KCG_BF16 ? 2 : 4, os = d->dtype_out == KCG_BF16 ? 2 : 4;
+  const size_t bh = static_cast<size_t>(d->B) * d->H;
+  const size_t ws_bytes = fmha_workspace_impl(d);
+  DevBuf q, k, v, o, ws;
+  KCG_CUDA_TRY(q.alloc(bh * d->Sq * d->D * es));
+  KCG_CUDA_TRY(k.alloc(bh * d->Skv * d->D * es));
+  KCG_CUDA_TRY(v.alloc(bh * d->Skv * d->D * es));
+  KCG_CUDA_TRY(o.alloc(bh * d->Sq * d->D * os));
+  KCG_CUDA_TRY(ws.alloc(ws_bytes));
+  KCG_CUDA_TRY(cudaMemset(q.p, 0, bh * d->Sq * d->D * es));
+  KCG_CUDA_TRY(cudaMemset(k.p, 0, bh * d->Skv * d->D * es));
+  KCG_CUDA_TRY(cudaMemset(v.p, 0, bh * d->Skv * d->D * es));
+  return time_launches([&] { return fmha_launch_impl(d, q.p, k.p, v.p, o.p, ws.p, ws_bytes, nullptr); }, iters,
+                       ms_per_launch);
 }
 
 kcg_status_t kcg_selftest_wait_timeout(uint32_t iterations) {

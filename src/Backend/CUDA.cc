@@ -157,6 +157,21 @@ kcg_status_t launchModule(mlir::ModuleOp& module, const std::vector<void*>& buff
   return KCG_OK;
 }
 
+float timeModule(mlir::ModuleOp& module, int iters) {
+  float total = 0.f;
+  bool any = false;
+  for (auto& p : planLaunches(module)) {
+    if (p.status != KCG_OK) return -1.f;
+    float ms = 0.f;
+    const kcg_status_t st = p.kind == LaunchPlan::Kind::Gemm ? kcg_gemm_time(&p.gemm, iters, &ms)
+                                                             : kcg_fmha_time(&p.fmha, iters, &ms);
+    if (st != KCG_OK) return -1.f;
+    total += ms;
+    any = true;
+  }
+  return any ? total : -1.f;
+}
+
 std::string CUDAGen(mlir::ModuleOp& module) {
   std::ostringstream os;
   os << "// Launcher for graph @" << module.getName() << ": the kernels are the hand-written sm_100a kernels of\n"

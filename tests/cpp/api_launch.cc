@@ -122,6 +122,22 @@ int main(int argc, char** argv) {
     writeFile(out + "/fa_o.bin", hO);
     cudaFree(dQ); cudaFree(dK); cudaFree(dV); cudaFree(dO); cudaFree(ws);
   }
+  // ---- configuration search with a real cost function ---------------------------------------------
+  {
+    auto graph = generator.createGraph("matmul_search");
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{2048, 1024}, std::string{"float32"});
+    auto B = graph.create<PlaceHolder>(std::vector<int64_t>{1024, 2048}, std::string{"float32"});
+    auto C = graph.create<Matmul>(A, B, MemorySpace::global);
+    (void)C;
+    auto wide = generator.matmulConfigList()[0];
+    wide["BLOCK_SIZE_N"] = 256;
+    generator.matmulConfigList().push_back(wide);   // two candidates: BLOCK_SIZE_N = 128 and 256
+    auto module = generator.optimize(graph);
+    const float ms = generator.evaluate(module);
+    auto plans = planLaunches(module);
+    std::cout << "evaluate_ms " << ms << " chosen_tile_n " << plans[0].gemm.tile_n << "\n";
+    generator.matmulConfigList().pop_back();
+  }
   std::cout << "ok\n";
   return 0;
 }

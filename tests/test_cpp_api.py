@@ -165,6 +165,8 @@ def test_cpp_api_launches_on_gpu(cuda_device, tmp_path):
                           ["-I/usr/local/cuda/include", "-L/usr/local/cuda/lib64", "-lcudart"])
     res = subprocess.run([str(exe), str(tmp_path)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
     assert res.returncode == 0, res.stdout
+    m = re.search(r"evaluate_ms ([0-9.e+-]+) chosen_tile_n (\d+)", res.stdout)
+    assert m and float(m.group(1)) > 0 and int(m.group(2)) in (128, 256)   # evaluate() measured something
     rd = lambda n, shape: np.fromfile(tmp_path / n, dtype=np.float32).reshape(shape)
     a, b, c = rd("mm_a.bin", (512, 256)), rd("mm_b.bin", (256, 384)), rd("mm_c.bin", (512, 384))
     want = oracle.matmul_relu(a, b)

@@ -210,3 +210,21 @@ def test_bounded_wait_reports_timeout_and_context_survives(cuda_device):
     a = uniform((128, 64), 1).to(cuda_device)
     b = uniform((64, 128), 2).to(cuda_device)
     assert rel_err(ops.matmul(a, b).cpu().numpy(), oracle.matmul(a.cpu().numpy(), b.cpu().numpy())) <= FP32_TOL
+
+
+def test_harness_log_is_readable_like_the_reference_log(cuda_device):
+    """The run-and-compare harness prints the reference's log format (performance/output.log)
+    and its lines parse back with the plot script's field positions."""
+    import io
+
+    from kernelcodegen_b200 import harness
+
+    buf = io.StringIO()
+    r0 = harness.run_case(4096, 2048, 1024, True, out=buf)
+    r1 = harness.run_case(512, 512, 512, True, out=buf)
+    text = buf.getvalue()
+    assert "My Matmul Latency = " in text and "cublas Ratio(TT) = " in text and " --- K --- : 1024" in text
+    rows = harness.parse_log(text)
+    assert len(rows) == 2 and all(all(x and x > 0 for x in row) for row in rows)
+    assert abs(rows[0][0] - r0["mine_ms"]) / r0["mine_ms"] < 1e-3
+    assert r0["rel_err"] <= FP32_TOL and r1["rel_err"] <= FP32_TOL
