@@ -84,7 +84,10 @@ typedef struct kcg_gemm_desc {
    * peer_c[i] + the same offset, i = 0..n_peers-1 (peer-mapped device pointers of the other
    * ranks' C buffers, already offset to this rank's row block). Plain stores, no multicast. */
   int32_t n_peers;
-  int32_t reserved;
+  /* 1: one CTA per 128 x tile_n tile.  2: CTA pairs (tcgen05 cta_group::2) share a
+   * 256 x tile_n tile, each CTA loading half of the B tile.  0: library default (pairs when
+   * M > 128). */
+  int32_t cta_group;
   void* peer_c[8];
 } kcg_gemm_desc;
 

@@ -63,7 +63,7 @@ class GemmDesc(Structure):
         ("dtype_in", c_int32), ("dtype_out", c_int32),
         ("precision", c_int32), ("epilogue", c_int32), ("b_layout", c_int32),
         ("tile_n", c_int32), ("stages", c_int32), ("group_m", c_int32),
-        ("n_peers", c_int32), ("reserved", c_int32),
+        ("n_peers", c_int32), ("cta_group", c_int32),
         ("peer_c", c_void_p * 8),
     ]
 

@@ -54,7 +54,7 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
 def matmul(a: torch.Tensor, b: torch.Tensor, *, relu: bool = False, precision: Optional[str] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
            b_col_major: bool = False, tile_n: int = 0, stages: int = 0, group_m: int = 0,
-           peers: Sequence[int] = ()) -> torch.Tensor:
+           cta_group: int = 0, peers: Sequence[int] = ()) -> torch.Tensor:
     """C = A . B (optionally ReLU'd).  A is [M, K] row-major; B is [K, N] row-major, or
     [N, K] when `b_col_major` (the reference's Layout::colMajor).  fp32 inputs use the
     3xTF32 path unless `precision="tf32"`; bf16 inputs use the bf16 path.
@@ -91,6 +91,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, relu: bool = False, precision: O
     d.epilogue = capi.KCG_EPI_RELU if relu else capi.KCG_EPI_NONE
     d.b_layout = capi.KCG_COL_MAJOR if b_col_major else capi.KCG_ROW_MAJOR
     d.tile_n, d.stages, d.group_m = tile_n, stages, group_m
+    d.cta_group = cta_group
     d.n_peers = len(peers)
     for i, p in enumerate(peers):
         d.peer_c[i] = p

@@ -50,9 +50,11 @@ def test_fp32_contract_small_shapes(cuda_device, m, n, k, b_col_major):
     want = oracle.matmul_relu(a.numpy(), b.numpy())
     bd = b.t().contiguous() if b_col_major else b
     for tile_n in (128, 256):
-        got = ops.matmul_relu(a.to(cuda_device), bd.to(cuda_device), b_col_major=b_col_major, tile_n=tile_n)
-        assert rel_err(got.cpu().numpy(), want) <= FP32_TOL
-        assert (got >= 0).all()
+        for cta_group in (1, 2):   # single CTAs and CTA pairs (tcgen05 cta_group::2)
+            got = ops.matmul_relu(a.to(cuda_device), bd.to(cuda_device), b_col_major=b_col_major, tile_n=tile_n,
+                                  cta_group=cta_group)
+            assert rel_err(got.cpu().numpy(), want) <= FP32_TOL
+            assert (got >= 0).all()
     plain = ops.matmul(a.to(cuda_device), bd.to(cuda_device), b_col_major=b_col_major)
     assert rel_err(plain.cpu().numpy(), oracle.matmul(a.numpy(), b.numpy())) <= FP32_TOL
     assert ops.last_device_status() == 0
@@ -68,11 +70,12 @@ def test_bf16_small_shapes(cuda_device, m, n, k, b_col_major, out_dtype):
     want = oracle.matmul_relu(a.float().numpy(), b.float().numpy())
     bd = b.t().contiguous() if b_col_major else b
     for tile_n in (128, 256):
-        got = ops.matmul_relu(a.to(cuda_device), bd.to(cuda_device), b_col_major=b_col_major, tile_n=tile_n,
-                              out_dtype=out_dtype)
-        assert got.dtype == out_dtype
-        tol = BF16_TOL if out_dtype == torch.bfloat16 else 5e-5  # fp32 output: exact products, fp32 sums
-        assert rel_err(got.float().cpu().numpy(), want) <= tol
+        for cta_group in (1, 2):
+            got = ops.matmul_relu(a.to(cuda_device), bd.to(cuda_device), b_col_major=b_col_major, tile_n=tile_n,
+                                  out_dtype=out_dtype, cta_group=cta_group)
+            assert got.dtype == out_dtype
+            tol = BF16_TOL if out_dtype == torch.bfloat16 else 5e-5  # fp32 output: exact products, fp32 sums
+            assert rel_err(got.float().cpu().numpy(), want) <= tol
     assert ops.last_device_status() == 0
 
 
@@ -104,8 +107,9 @@ def test_config_fuse_matmul_relu_4096x1024x2048(cuda_device):
     assert torch.equal(c, torch.clamp_min(plain, 0))
     # linearity in A (size-independent property): (2A).B == 2(A.B) exactly in binary fp
     assert torch.equal(ops.matmul(ad * 2, bd), plain * 2)
-    # both tile widths agree to rounding
+    # both tile widths, single CTAs and CTA pairs agree to rounding
     assert rel_err(ops.matmul_relu(ad, bd, tile_n=256).cpu().numpy(), c.cpu().numpy()) <= 1e-5
+    assert rel_err(ops.matmul_relu(ad, bd, cta_group=1).cpu().numpy(), c.cpu().numpy()) <= 1e-5
     assert ops.last_device_status() == 0
 
 
