@@ -7,8 +7,10 @@
 // returns a small launcher translation unit -- `namespace <graph> { kernel0(...) }` as before,
 // but the body fills a descriptor and calls kcg_gemm_launch / kcg_fmha_fwd_launch -- so that
 // `save()` still writes something a harness can compile.  `launchModule` does the same calls
-// directly.  There is deliberately no generic affine->CUDA emitter: an unscheduled or
-// unsupported function yields KCG_UNSUPPORTED, never a fallback kernel.
+// directly.  BatchedMatmul and Softmax functions that are not part of an attention chain are
+// dispatched as they stand to the batched GEMM and the row-softmax kernel.  There is
+// deliberately no generic affine->CUDA emitter: any other unscheduled function yields
+// KCG_UNSUPPORTED, never a fallback kernel.
 #pragma once
 
 #include <string>
@@ -21,12 +23,16 @@ namespace KernelCodeGen {
 
 // One kernel launch derived from a `func.call` of a function with func.state = "gpu".
 struct LaunchPlan {
-  enum class Kind { Gemm, Fmha } kind = Kind::Gemm;
+  enum class Kind { Gemm, Fmha, BatchedGemm, Softmax } kind = Kind::Gemm;
   std::string function;            // callee symbol
   kcg_gemm_desc gemm{};
   kcg_fmha_desc fmha{};
+  // BatchedGemm: `gemm` describes one product; batch count and element strides between products.
+  int64_t batch = 1, strideA = 0, strideB = 0, strideC = 0;
+  // Softmax: [rows, cols] fp32, in place on its single buffer.
+  int64_t rows = 0, cols = 0;
   // Position (among the module-level memref.alloc ops, in program order) of each pointer
-  // argument, in the kernel's argument order: (A, B, C) or (Q, K, V, O).
+  // argument, in the kernel's argument order: (A, B, C), (Q, K, V, O) or (X) for Softmax.
   std::vector<int> buffers;
   kcg_status_t status = KCG_OK;    // KCG_UNSUPPORTED when the schedule has no kernel
   std::string why;

@@ -149,6 +149,19 @@ kcg_status_t kcg_fmha_fwd_launch(const kcg_fmha_desc* d, const void* Q, const vo
                                  const void* V, void* O, void* workspace, size_t workspace_bytes,
                                  void* stream);
 
+/* The reference's Softmax operator on its own (src/Frontend/Operators.cc:474-536): last-axis
+ * exp(x)/sum(exp(x)) over a [rows, cols] fp32 array, in place when y == x.  Used for graphs
+ * where Softmax is not part of an attention chain (there it is fused into the FMHA kernel). */
+kcg_status_t kcg_softmax_launch(int64_t rows, int64_t cols, const void* x, void* y, void* stream);
+
+/* The reference's BatchedMatmul operator on its own (src/Frontend/Operators.cc:253-420): `batch`
+ * independent products described by `d`, operand i at base + i * stride (strides in elements;
+ * 0 broadcasts an operand).  Layout::colMajor B = d->b_layout KCG_COL_MAJOR.  One GEMM launch per
+ * batch entry on `stream`; the workspace is shared (the launches are stream-ordered). */
+kcg_status_t kcg_batched_gemm_launch(const kcg_gemm_desc* d, int64_t batch, int64_t stride_a, int64_t stride_b,
+                                     int64_t stride_c, const void* A, const void* B, void* C, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+
 /* Host-buffer convenience forms (what the reference's absent harness did around the kernel:
  * cudaMalloc, H2D, launch, D2H -- performance/output.log:6-13).  They allocate device
  * buffers, copy, launch on `stream`, copy back and synchronise. */

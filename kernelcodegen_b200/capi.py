@@ -37,6 +37,8 @@ EXPORTED_SYMBOLS = (
     "kcg_gemm_launch",
     "kcg_gemm_launch_static",
     "kcg_fmha_fwd_launch",
+    "kcg_softmax_launch",
+    "kcg_batched_gemm_launch",
     "kcg_gemm_host",
     "kcg_fmha_fwd_host",
     "kcg_gemm_time",
@@ -107,6 +109,11 @@ def load() -> ctypes.CDLL:
     lib.kcg_gemm_launch_static.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p]
     lib.kcg_fmha_fwd_launch.restype = c_int
     lib.kcg_fmha_fwd_launch.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.kcg_softmax_launch.restype = c_int
+    lib.kcg_softmax_launch.argtypes = [c_int64, c_int64, c_void_p, c_void_p, c_void_p]
+    lib.kcg_batched_gemm_launch.restype = c_int
+    lib.kcg_batched_gemm_launch.argtypes = [POINTER(GemmDesc), c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_size_t, c_void_p]
     lib.kcg_gemm_host.restype = c_int
     lib.kcg_gemm_host.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p]
     lib.kcg_fmha_fwd_host.restype = c_int

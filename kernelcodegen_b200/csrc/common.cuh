@@ -44,5 +44,6 @@ kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, cons
 kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void* K, const void* V,
                               void* O, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t fmha_workspace_impl(const kcg_fmha_desc* d);
+kcg_status_t softmax_launch_impl(long long rows, long long cols, const void* x, void* y, cudaStream_t stream);
 
 }  // namespace kcg

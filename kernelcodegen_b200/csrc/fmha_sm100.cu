@@ -446,13 +446,28 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// fp32 -> bf16 (round to nearest even), n4 = element count / 4
-__global__ void f32_to_bf16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst,
-                                   long long n4) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+// fp32 -> bf16 (round to nearest even) of Q, K and V in one launch; counts in float4 units
+struct CastArgs {
+  const float4* src[3];
+  uint2* dst[3];
+  long long n4[3];
+};
+__global__ void f32_to_bf16_kernel(CastArgs a) {
+  const long long total = a.n4[0] + a.n4[1] + a.n4[2];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float4 v = src[i];
-    dst[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    int t = 0;
+    long long k = i;
+    if (k >= a.n4[0]) {
+      k -= a.n4[0];
+      t = 1;
+      if (k >= a.n4[1]) {
+        k -= a.n4[1];
+        t = 2;
+      }
+    }
+    const float4 v = a.src[t][k];
+    a.dst[t][k] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
   }
 }
 
@@ -506,13 +521,17 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
     void* kb = w + pad256(q_elems * 2);
     void* vb = w + pad256(q_elems * 2) + pad256(kv_elems * 2);
     const int blocks = device_sm_count() * 4;
-    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(Q),
-                                                    static_cast<uint2*>(qb), q_elems / 4);
-    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(K),
-                                                    static_cast<uint2*>(kb), kv_elems / 4);
-    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(V),
-                                                    static_cast<uint2*>(vb), kv_elems / 4);
-    g_launches.fetch_add(3);
+    CastArgs ca;
+    ca.src[0] = static_cast<const float4*>(Q);
+    ca.src[1] = static_cast<const float4*>(K);
+    ca.src[2] = static_cast<const float4*>(V);
+    ca.dst[0] = static_cast<uint2*>(qb);
+    ca.dst[1] = static_cast<uint2*>(kb);
+    ca.dst[2] = static_cast<uint2*>(vb);
+    ca.n4[0] = static_cast<long long>(q_elems / 4);
+    ca.n4[1] = ca.n4[2] = static_cast<long long>(kv_elems / 4);
+    f32_to_bf16_kernel<<<blocks, 256, 0, stream>>>(ca);
+    g_launches.fetch_add(1);
     KCG_CUDA_TRY(cudaGetLastError());
     q = qb;
     k = kb;

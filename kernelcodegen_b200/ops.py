@@ -146,6 +146,57 @@ def fmha(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float = 1.
     return out
 
 
+def softmax(x: torch.Tensor, *, inplace: bool = False) -> torch.Tensor:
+    """Last-axis softmax of an fp32 tensor (the reference's standalone Softmax operator)."""
+    dev = _require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise TypeError("softmax takes a contiguous float32 tensor")
+    y = x if inplace else torch.empty_like(x)
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    with torch.cuda.device(dev):
+        st = capi.load().kcg_softmax_launch(rows, cols, x.data_ptr(), y.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    capi.check(st, "kcg_softmax_launch")
+    return y
+
+
+def batched_matmul(a: torch.Tensor, b: torch.Tensor, *, b_col_major: bool = False, precision: Optional[str] = None,
+                   relu: bool = False) -> torch.Tensor:
+    """C[..., m, n] = A[..., m, k] . B[..., k, n]  (B[..., n, k] when `b_col_major`): the
+    reference's standalone BatchedMatmul operator; leading dimensions are batch dimensions."""
+    dev = _require_cuda(a, b)
+    if a.dim() < 2 or a.dim() != b.dim() or a.shape[:-2] != b.shape[:-2]:
+        raise ValueError("A and B need equal batch dimensions")
+    if not (a.is_contiguous() and b.is_contiguous()) or a.dtype != b.dtype:
+        raise ValueError("A and B must be contiguous and share a dtype")
+    m, k = a.shape[-2:]
+    n, kb = (b.shape[-2], b.shape[-1]) if b_col_major else (b.shape[-1], b.shape[-2])
+    if k != kb:
+        raise ValueError("inner dimensions differ")
+    batch = 1
+    for s_ in a.shape[:-2]:
+        batch *= s_
+    out = torch.empty(a.shape[:-2] + (m, n), dtype=a.dtype, device=dev)
+    if precision is None:
+        precision = "bf16" if a.dtype == torch.bfloat16 else "3xtf32"
+    d = capi.GemmDesc()
+    d.M, d.N, d.K = m, n, k
+    d.lda, d.ldb, d.ldc = k, (k if b_col_major else n), n
+    d.dtype_in = d.dtype_out = _dtype_code(a.dtype)
+    d.precision = _PRECISIONS[precision]
+    d.epilogue = capi.KCG_EPI_RELU if relu else capi.KCG_EPI_NONE
+    d.b_layout = capi.KCG_COL_MAJOR if b_col_major else capi.KCG_ROW_MAJOR
+    lib = capi.load()
+    with torch.cuda.device(dev):
+        ws_bytes = lib.kcg_gemm_workspace_bytes(ctypes.byref(d))
+        ws = _workspace(dev, ws_bytes)
+        st = lib.kcg_batched_gemm_launch(ctypes.byref(d), batch, m * k, k * n, m * n, a.data_ptr(), b.data_ptr(),
+                                         out.data_ptr(), ws.data_ptr() if ws is not None else None, ws_bytes,
+                                         torch.cuda.current_stream(dev).cuda_stream)
+    capi.check(st, "kcg_batched_gemm_launch")
+    return out
+
+
 def last_device_status() -> int:
     """0, or the code of the bounded device-side wait that ran out (synchronises)."""
     return int(capi.load().kcg_last_device_status())

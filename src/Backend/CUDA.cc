@@ -64,6 +64,55 @@ std::vector<LaunchPlan> planLaunches(mlir::ModuleOp& module) {
     LaunchPlan p;
     p.function = callee->name;
     const std::string kind = callee->getStringAttr("kcg.op");
+    const bool is_bmm = callee->name.rfind("BatchMatmul_", 0) == 0 && op->operands.size() == 3;
+    const bool is_softmax = callee->name.rfind("Softmax_", 0) == 0 && op->operands.size() == 1;
+    if (kind.empty() && (is_bmm || is_softmax)) {
+      // library operators: dispatched from the naive nest as it stands
+      for (auto v : op->operands) p.buffers.push_back(allocIndex(module, underlyingBuffer(module, v)));
+      const auto t0 = op->operands[0].getType();
+      const int dt0 = dtypeCode(kcgir::scalarName(t0.elem));
+      if (is_softmax) {
+        p.kind = LaunchPlan::Kind::Softmax;
+        p.cols = t0.shape.back();
+        p.rows = 1;
+        for (size_t i = 0; i + 1 < t0.shape.size(); ++i) p.rows *= t0.shape[i];
+        if (dt0 != KCG_F32) {
+          p.status = KCG_UNSUPPORTED;
+          p.why = "standalone Softmax is float32 only";
+        }
+      } else {
+        p.kind = LaunchPlan::Kind::BatchedGemm;
+        const auto tA = op->operands[0].getType(), tB = op->operands[1].getType(), tC = op->operands[2].getType();
+        const std::string& nm = callee->name;
+        const bool transA = nm[nm.size() - 2] == 'T', transB = nm[nm.size() - 1] == 'T';
+        const size_t r = tC.shape.size();
+        auto& d = p.gemm;
+        d.M = tC.shape[r - 2];
+        d.N = tC.shape[r - 1];
+        d.K = tA.shape[r - 1];
+        d.lda = d.K;
+        d.ldb = transB ? d.K : d.N;
+        d.ldc = d.N;
+        d.dtype_in = d.dtype_out = dt0;
+        d.precision = dt0 == KCG_BF16 ? KCG_PREC_BF16 : KCG_PREC_3XTF32;
+        d.b_layout = transB ? KCG_COL_MAJOR : KCG_ROW_MAJOR;
+        p.batch = 1;
+        for (size_t i = 0; i + 2 < r; ++i) p.batch *= tC.shape[i];
+        p.strideA = d.M * d.K;
+        p.strideB = d.K * d.N;
+        p.strideC = d.M * d.N;
+        (void)tB;
+        if (transA) {
+          p.status = KCG_UNSUPPORTED;
+          p.why = "BatchedMatmul with a colMajor A operand has no kernel";
+        } else if (dt0 < 0) {
+          p.status = KCG_UNSUPPORTED;
+          p.why = "element type has no kernel (float32 and bfloat16 do)";
+        }
+      }
+      plans.push_back(p);
+      continue;
+    }
     if (callee->getStringAttr("func.state") != "gpu" || kind.empty()) {
       p.status = KCG_UNSUPPORTED;
       p.why = "function @" + callee->name + " has not been scheduled for the GPU (no generic code generator)";
@@ -128,8 +177,9 @@ size_t workspaceBytes(mlir::ModuleOp& module) {
   size_t need = 0;
   for (auto& p : planLaunches(module)) {
     if (p.status != KCG_OK) continue;
-    const size_t n = p.kind == LaunchPlan::Kind::Gemm ? kcg_gemm_workspace_bytes(&p.gemm)
-                                                      : kcg_fmha_workspace_bytes(&p.fmha);
+    size_t n = 0;
+    if (p.kind == LaunchPlan::Kind::Gemm || p.kind == LaunchPlan::Kind::BatchedGemm) n = kcg_gemm_workspace_bytes(&p.gemm);
+    else if (p.kind == LaunchPlan::Kind::Fmha) n = kcg_fmha_workspace_bytes(&p.fmha);
     need = n > need ? n : need;
   }
   return need;
@@ -148,6 +198,13 @@ kcg_status_t launchModule(mlir::ModuleOp& module, const std::vector<void*>& buff
     if (p.kind == LaunchPlan::Kind::Gemm) {
       if (ptr.size() != 3) return KCG_BAD_ARGUMENT;
       st = kcg_gemm_launch(&p.gemm, ptr[0], ptr[1], ptr[2], workspace, wsBytes, stream);
+    } else if (p.kind == LaunchPlan::Kind::BatchedGemm) {
+      if (ptr.size() != 3) return KCG_BAD_ARGUMENT;
+      st = kcg_batched_gemm_launch(&p.gemm, p.batch, p.strideA, p.strideB, p.strideC, ptr[0], ptr[1], ptr[2], workspace,
+                                   wsBytes, stream);
+    } else if (p.kind == LaunchPlan::Kind::Softmax) {
+      if (ptr.size() != 1) return KCG_BAD_ARGUMENT;
+      st = kcg_softmax_launch(p.rows, p.cols, ptr[0], ptr[0], stream);
     } else {
       if (ptr.size() != 4) return KCG_BAD_ARGUMENT;
       st = kcg_fmha_fwd_launch(&p.fmha, ptr[0], ptr[1], ptr[2], ptr[3], workspace, wsBytes, stream);
@@ -163,6 +220,7 @@ float timeModule(mlir::ModuleOp& module, int iters) {
   for (auto& p : planLaunches(module)) {
     if (p.status != KCG_OK) return -1.f;
     float ms = 0.f;
+    if (p.kind != LaunchPlan::Kind::Gemm && p.kind != LaunchPlan::Kind::Fmha) continue;  // fixed-cost library ops
     const kcg_status_t st = p.kind == LaunchPlan::Kind::Gemm ? kcg_gemm_time(&p.gemm, iters, &ms)
                                                              : kcg_fmha_time(&p.fmha, iters, &ms);
     if (st != KCG_OK) return -1.f;
@@ -183,6 +241,27 @@ std::string CUDAGen(mlir::ModuleOp& module) {
     os << "\n// func.call @" << p.function << "\n";
     if (p.status != KCG_OK) {
       os << "// not dispatched: " << p.why << "\n";
+      continue;
+    }
+    if (p.kind == LaunchPlan::Kind::Softmax) {
+      os << "inline kcg_status_t kernel" << kid << "(float* X, void*, size_t, cudaStream_t stream) {\n"
+         << "  return kcg_softmax_launch(" << p.rows << ", " << p.cols << ", X, X, stream);\n}\n";
+      ++kid;
+      continue;
+    }
+    if (p.kind == LaunchPlan::Kind::BatchedGemm) {
+      const auto& d = p.gemm;
+      const char* ct = d.dtype_in == KCG_BF16 ? "void" : "float";
+      os << "inline kcg_status_t kernel" << kid << "(const " << ct << "* A, const " << ct << "* B, " << ct
+         << "* C, void* workspace, size_t workspace_bytes, cudaStream_t stream) {\n"
+         << "  kcg_gemm_desc d = {};\n"
+         << "  d.M = " << d.M << "; d.N = " << d.N << "; d.K = " << d.K << ";\n"
+         << "  d.lda = " << d.lda << "; d.ldb = " << d.ldb << "; d.ldc = " << d.ldc << ";\n"
+         << "  d.dtype_in = " << d.dtype_in << "; d.dtype_out = " << d.dtype_out << "; d.precision = " << d.precision
+         << "; d.b_layout = " << d.b_layout << ";\n"
+         << "  return kcg_batched_gemm_launch(&d, " << p.batch << ", " << p.strideA << ", " << p.strideB << ", "
+         << p.strideC << ", A, B, C, workspace, workspace_bytes, stream);\n}\n";
+      ++kid;
       continue;
     }
     if (p.kind == LaunchPlan::Kind::Gemm) {

@@ -99,6 +99,26 @@ int main() {
               << plans[0].buffers[0] << plans[0].buffers[1] << plans[0].buffers[2] << plans[0].buffers[3] << "\n";
   }
 
+  // ---- BatchedMatmul / Softmax outside an attention chain: dispatched as library operators ------
+  {
+    auto graph = generator.createGraph("standalone_ops");
+    auto A = graph.create<PlaceHolder>(std::vector<int64_t>{3, 256, 64}, std::string{"float32"});
+    auto B = graph.create<PlaceHolder>(std::vector<int64_t>{3, 64, 128}, std::string{"float32"});
+    auto C = graph.create<BatchedMatmul>(A, Layout::rowMajor, B, Layout::rowMajor);
+    auto X = graph.create<PlaceHolder>(std::vector<int64_t>{5, 7, 300}, std::string{"float32"});
+    auto Y = graph.create<Softmax>(X, -1, MemorySpace::inplace);
+    (void)C;
+    (void)Y;
+    auto module = generator.optimize(graph);
+    stage("standalone_ops", module);
+    auto plans = planLaunches(module);
+    std::cout << "plans " << plans.size();
+    for (auto& p : plans) std::cout << " kind " << static_cast<int>(p.kind) << " status " << p.status;
+    std::cout << " batch " << plans[0].batch << " M " << plans[0].gemm.M << " N " << plans[0].gemm.N << " K "
+              << plans[0].gemm.K << " rows " << plans[1].rows << " cols " << plans[1].cols << "\n";
+    std::cout << "=== codegen_standalone\n" << generator.codegen(module);
+  }
+
   // ---- error behaviour -------------------------------------------------------------------------
   {
     auto graph = generator.createGraph("errors");

@@ -121,6 +121,14 @@ def test_fmha_chain_is_fused(stages):
     assert "plans 1 status 0 B 8 H 32 S 2048 D 64 buffers 0124" in code
 
 
+def test_standalone_batched_matmul_and_softmax_are_dispatched(stages):
+    t = stages["standalone_ops"]
+    assert "BatchMatmul_3_m256_n128_k64_NN" in t and "Softmax_5_7_300_axis2" in t
+    assert "plans 2 kind 2 status 0 kind 3 status 0 batch 3 M 256 N 128 K 64 rows 35 cols 300" in t
+    code = stages["codegen_standalone"]
+    assert "kcg_batched_gemm_launch(&d, 3, 16384, 8192, 32768" in code and "kcg_softmax_launch(35, 300, X, X, stream)" in code
+
+
 def test_error_behaviour(stages):
     t = stages["errors"]
     assert "mismatch_is_null 1" in t and "bad_dtype_is_null 1" in t
@@ -131,7 +139,7 @@ def test_generated_launcher_text_compiles(stages, tmp_path):
     cuda_inc = Path("/usr/local/cuda/include")
     if not cuda_inc.exists():
         pytest.skip("CUDA headers not installed")
-    for name in ("codegen_matmul_relu", "codegen_fmha"):
+    for name in ("codegen_matmul_relu", "codegen_fmha", "codegen_standalone"):
         text = stages[name].split("\nplans ")[0]
         src = tmp_path / f"{name}.cc"
         src.write_text(text + "\nint main() { return 0; }\n")

@@ -1,0 +1,68 @@
+"""GPU parity of the standalone BatchedMatmul and Softmax operators (the reference's Frontend
+ops used outside an attention chain) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(x, ref):
+    x = np.asarray(x, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(x - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.mark.parametrize("shape", [(5, 7, 33), (4, 128), (3, 1000), (2, 3, 1024), (6, 4100), (1, 1), (2, 8192)])
+def test_softmax_matches_oracle(cuda_device, shape):
+    from kernelcodegen_b200 import ops
+
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g) * 3
+    want = oracle.softmax(x.numpy())
+    got = ops.softmax(x.to(cuda_device))
+    assert rel_err(got.cpu().numpy(), want) <= 1e-5
+    np.testing.assert_allclose(got.sum(-1).cpu().numpy(), 1.0, atol=1e-5)
+    xin = x.to(cuda_device).clone()
+    assert ops.softmax(xin, inplace=True) is xin
+    assert rel_err(xin.cpu().numpy(), want) <= 1e-5
+
+
+def test_softmax_golden(cuda_device, golden):
+    from kernelcodegen_b200 import ops
+
+    got = ops.softmax(torch.from_numpy(golden["sm_x"]).to(cuda_device))
+    assert rel_err(got.cpu().numpy(), golden["sm_y"]) <= 1e-5
+
+
+@pytest.mark.parametrize("b_col_major", [False, True])
+def test_batched_matmul_matches_oracle(cuda_device, b_col_major):
+    from kernelcodegen_b200 import ops
+
+    g = torch.Generator().manual_seed(7)
+    a = torch.rand((2, 3, 200, 72), generator=g) * 2 - 1
+    b = torch.rand((2, 3, 136, 72) if b_col_major else (2, 3, 72, 136), generator=g) * 2 - 1
+    want = oracle.batched_matmul(a.numpy(), b.numpy(), b_col_major=b_col_major)
+    got = ops.batched_matmul(a.to(cuda_device), b.to(cuda_device), b_col_major=b_col_major)
+    assert rel_err(got.cpu().numpy(), want) <= 1e-4
+    gb = ops.batched_matmul(a.bfloat16().to(cuda_device), b.bfloat16().to(cuda_device), b_col_major=b_col_major)
+    wantb = oracle.batched_matmul(a.bfloat16().float().numpy(), b.bfloat16().float().numpy(), b_col_major=b_col_major)
+    assert rel_err(gb.float().cpu().numpy(), wantb) <= 2e-2
+    assert ops.last_device_status() == 0
+
+
+def test_unfused_attention_graph_equals_fused_kernel(cuda_device):
+    """BatchedMatmul(Q, K^T) -> Softmax -> BatchedMatmul(P, V) run operator by operator gives the
+    fused FMHA kernel's answer (to the bf16 bar of the fused kernel)."""
+    from kernelcodegen_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn((1, 2, 256, 64), generator=g).to(cuda_device) * s for s in (0.4, 0.4, 1.0))
+    p = ops.softmax(ops.batched_matmul(q, k, b_col_major=True), inplace=True)
+    o_graph = ops.batched_matmul(p, v)
+    o_fused = ops.fmha(q, k, v, scale=1.0)
+    want = oracle.fmha(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+    assert rel_err(o_graph.cpu().numpy(), want) <= 1e-4          # fp32-contract operators
+    assert rel_err(o_fused.cpu().numpy(), o_graph.cpu().numpy()) <= 2e-2
