@@ -65,7 +65,8 @@ typedef enum kcg_layout_t { KCG_ROW_MAJOR = 0, KCG_COL_MAJOR = 1 } kcg_layout_t;
  * (src/Frontend/Operators.cc:77-179) + Relu::build (:182-250) by MatmulOptimizer
  * (src/Optimizer/Optimizer.cc:383-548).  Leading dimensions are in ELEMENTS.
  * tile_n / stages / group_m are the schedule knobs (0 = library default):
- *   tile_n  <- BLOCK_SIZE_N (128 or 256),  tile_m is fixed at 128 (one UMMA M),
+ *   tile_n  <- BLOCK_SIZE_N (128 or 256; default 256, 128 for short 3xTF32 launches),
+ *              tile_m is fixed at 128 (one UMMA M) per CTA,
  *   stages  <- depth of the TMA->UMMA shared-memory ring,
  *   group_m <- GROUP_SIZE_M: how many row-blocks are walked before moving to the next
  *              column-block (L2 reuse of the B panel). */
@@ -85,8 +86,8 @@ typedef struct kcg_gemm_desc {
    * ranks' C buffers, already offset to this rank's row block). Plain stores, no multicast. */
   int32_t n_peers;
   /* 1: one CTA per 128 x tile_n tile.  2: CTA pairs (tcgen05 cta_group::2) share a
-   * 256 x tile_n tile, each CTA loading half of the B tile.  0: library default (pairs when
-   * M > 128). */
+   * 256 x tile_n tile, each CTA loading half of the B tile.  0: library default (pairs for launches
+   * below ~4 TFLOP of work, single CTAs for long, power-limited ones). */
   int32_t cta_group;
   void* peer_c[8];
 } kcg_gemm_desc;

@@ -763,13 +763,18 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   if ((d->lda * es) % 16 || (d->ldb * es) % 16 || (d->ldc * os) % 16) return KCG_BAD_ALIGN;
   for (int i = 0; i < d->n_peers; ++i)
     if (!d->peer_c[i] || !aligned16(d->peer_c[i])) return KCG_BAD_ALIGN;
+  // Defaults, from interleaved measurements on one B200 under its 1000 W power cap:
+  //  - short launches (< ~4 TFLOP of work) run faster on CTA pairs (bf16 4096^3 +8 %, 8192^3 +4 %;
+  //    3xTF32 with 128-wide tiles +15..30 % on 4096x2048x1024 and 4096^3);
+  //  - long launches are power-limited, and there the pair kernel sustains lower clocks
+  //    (bf16 16384^3 -3.5 %, 32768^3 -19 %), so single CTAs with 256-wide tiles are used.
+  const double work = 2.0 * static_cast<double>(d->M) * static_cast<double>(d->N) * static_cast<double>(d->K);
+  const bool small_job = work < 4e12;
   int bn = d->tile_n;
-  if (bn == 0) bn = (kind == 2) ? 128 : 256;
+  if (bn == 0) bn = (kind == 2 && small_job) ? 128 : 256;
   if (bn != 128 && bn != 256) return KCG_UNSUPPORTED;
   if (d->cta_group != 0 && d->cta_group != 1 && d->cta_group != 2) return KCG_UNSUPPORTED;
-  // default (0): CTA pairs whenever the problem has at least two 128-row blocks -- measured
-  // faster than single CTAs for every precision (bf16 256-wide tiles: +9 %; 3xTF32 128-wide: +15-30 %)
-  const bool pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM);
+  const bool pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM && small_job);
 
   const void* pa = A;
   const void* pb = B;
