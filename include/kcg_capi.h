@@ -163,10 +163,27 @@ kcg_status_t kcg_batched_gemm_launch(const kcg_gemm_desc* d, int64_t batch, int6
                                      int64_t stride_c, const void* A, const void* B, void* C, void* workspace,
                                      size_t workspace_bytes, void* stream);
 
-/* Host-buffer convenience forms (what the reference's absent harness did around the kernel:
- * cudaMalloc, H2D, launch, D2H -- performance/output.log:6-13).  They allocate device
- * buffers, copy, launch on `stream`, copy back and synchronise. */
+/* Host-buffer forms (what the reference's absent harness did around the kernel: cudaMalloc, H2D,
+ * launch, D2H -- performance/output.log:6-13).  They allocate device buffers, copy, launch, copy
+ * back and synchronise.  kcg_gemm_host runs the schedule of kcg_gemm_host_staged below. */
 kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC);
+
+/* The same host-to-host product with the PCIe copies overlapped with the kernel, on device buffers
+ * the caller owns (no allocation here).  hA/hB/hC are host arrays laid out as `d` says (pinned
+ * memory for the copies to overlap; pageable memory works but serialises); dA/dB/dC are device
+ * arrays of the same shapes and leading dimensions.  A is cut into row chunks and B into column
+ * chunks (`chunks` of each, at most 16; 0 = about 2048 rows / columns per chunk), copied
+ * alternately; the kernel runs on row chunk k x column chunks 0..k-1 as soon as row chunk k has
+ * landed and on row chunks 0..k x column chunk k as soon as column chunk k has, so every C tile
+ * is computed once, as early as its operands allow; finished strips of C return to the host while
+ * later chunks are still arriving.  Copies and launches run on the library's own three streams per
+ * device; they start after the work already queued on `stream`, and `stream` continues once the
+ * last strip of C is on the host, so the caller only synchronises `stream`.  d->peer_c, when set,
+ * receives every strip as in kcg_gemm_launch.  `workspace` as for kcg_gemm_launch with `d`.
+ * The device-side status is not read here: call kcg_last_device_status after synchronising. */
+kcg_status_t kcg_gemm_host_staged(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC, void* dA,
+                                  void* dB, void* dC, void* workspace, size_t workspace_bytes, int chunks,
+                                  void* stream);
 kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const void* hK,
                                const void* hV, void* hO);
 

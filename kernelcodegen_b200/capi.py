@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "kcg_softmax_launch",
     "kcg_batched_gemm_launch",
     "kcg_gemm_host",
+    "kcg_gemm_host_staged",
     "kcg_fmha_fwd_host",
     "kcg_gemm_time",
     "kcg_fmha_time",
@@ -116,6 +117,9 @@ def load() -> ctypes.CDLL:
                                             c_void_p, c_void_p, c_size_t, c_void_p]
     lib.kcg_gemm_host.restype = c_int
     lib.kcg_gemm_host.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p]
+    lib.kcg_gemm_host_staged.restype = c_int
+    lib.kcg_gemm_host_staged.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_size_t, c_int, c_void_p]
     lib.kcg_fmha_fwd_host.restype = c_int
     lib.kcg_fmha_fwd_host.argtypes = [POINTER(FmhaDesc), c_void_p, c_void_p, c_void_p, c_void_p]
     lib.kcg_gemm_time.restype = c_int

@@ -181,13 +181,20 @@ kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* h
   KCG_CUDA_TRY(b.alloc(b_bytes));
   KCG_CUDA_TRY(c.alloc(c_bytes));
   KCG_CUDA_TRY(ws.alloc(ws_bytes));
-  KCG_CUDA_TRY(cudaMemcpy(a.p, hA, a_bytes, cudaMemcpyHostToDevice));
-  KCG_CUDA_TRY(cudaMemcpy(b.p, hB, b_bytes, cudaMemcpyHostToDevice));
-  if (d->ldc != d->N) KCG_CUDA_TRY(cudaMemcpy(c.p, hC, c_bytes, cudaMemcpyHostToDevice));
-  kcg_status_t st = gemm_launch_impl(d, a.p, b.p, c.p, ws.p, ws_bytes, nullptr);
-  if (st != KCG_OK) return st;
-  KCG_CUDA_TRY(cudaMemcpy(hC, c.p, c_bytes, cudaMemcpyDeviceToHost));
+  kcg_status_t st = gemm_host_staged_impl(d, hA, hB, hC, a.p, b.p, c.p, ws.p, ws_bytes, 0, nullptr);
+  if (st != KCG_OK) {
+    cudaDeviceSynchronize();  // nothing may still use the buffers when they are freed
+    return st;
+  }
+  KCG_CUDA_TRY(cudaStreamSynchronize(nullptr));
   return kcg_last_device_status() ? KCG_DEVICE_TIMEOUT : KCG_OK;
+}
+
+kcg_status_t kcg_gemm_host_staged(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC, void* dA,
+                                  void* dB, void* dC, void* workspace, size_t workspace_bytes, int chunks,
+                                  void* stream) {
+  return gemm_host_staged_impl(d, hA, hB, hC, dA, dB, dC, workspace, workspace_bytes, chunks,
+                               static_cast<cudaStream_t>(stream));
 }
 
 kcg_status_t kcg_fmha_fwd_host(const kcg_fmha_desc* d, const void* hQ, const void* hK,

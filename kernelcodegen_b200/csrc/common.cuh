@@ -41,6 +41,9 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
 size_t gemm_workspace_impl(const kcg_gemm_desc* d);
 kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                                      cudaStream_t stream);
+kcg_status_t gemm_host_staged_impl(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC, void* dA,
+                                   void* dB, void* dC, void* ws, size_t ws_bytes, int chunks,
+                                   cudaStream_t stream);
 kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void* K, const void* V,
                               void* O, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t fmha_workspace_impl(const kcg_fmha_desc* d);

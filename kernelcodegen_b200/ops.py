@@ -106,6 +106,48 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, relu: bool = False, precision: O
     return out
 
 
+def matmul_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor, a_dev: torch.Tensor,
+                b_dev: torch.Tensor, c_dev: torch.Tensor, *, relu: bool = False, precision: Optional[str] = None,
+                b_col_major: bool = False, chunks: int = 0, peers: Sequence[int] = ()) -> torch.Tensor:
+    """c_host = A . B from HOST arrays (pin them for the copies to overlap), staged through the
+    caller's device arrays of the same shapes: row chunks of A and column chunks of B are copied
+    while the kernel already runs on the tiles that have arrived, and finished strips of C return
+    to the host meanwhile (`kcg_gemm_host_staged`).  Asynchronous: synchronise the current stream
+    before reading `c_host`."""
+    dev = _require_cuda(a_dev, b_dev, c_dev)
+    for h, t in ((a_host, a_dev), (b_host, b_dev), (c_host, c_dev)):
+        if h.is_cuda or h.shape != t.shape or h.dtype != t.dtype or h.stride() != t.stride():
+            raise ValueError("host and device arrays must match in shape, dtype and strides")
+        if h.dim() != 2 or h.stride(1) != 1:
+            raise ValueError("2-D row-contiguous arrays expected")
+    M, K = a_dev.shape
+    N = b_dev.shape[0] if b_col_major else b_dev.shape[1]
+    if (b_dev.shape[1] if b_col_major else b_dev.shape[0]) != K or c_dev.shape != (M, N):
+        raise ValueError("shapes do not form a product")
+    if precision is None:
+        precision = "bf16" if a_dev.dtype == torch.bfloat16 else "3xtf32"
+    d = capi.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.lda, d.ldb, d.ldc = a_dev.stride(0), b_dev.stride(0), c_dev.stride(0)
+    d.dtype_in, d.dtype_out = _dtype_code(a_dev.dtype), _dtype_code(c_dev.dtype)
+    d.precision = _PRECISIONS[precision]
+    d.epilogue = capi.KCG_EPI_RELU if relu else capi.KCG_EPI_NONE
+    d.b_layout = capi.KCG_COL_MAJOR if b_col_major else capi.KCG_ROW_MAJOR
+    d.n_peers = len(peers)
+    for i, p in enumerate(peers):
+        d.peer_c[i] = p
+    lib = capi.load()
+    with torch.cuda.device(dev):
+        ws_bytes = lib.kcg_gemm_workspace_bytes(ctypes.byref(d))
+        ws = _workspace(dev, ws_bytes)
+        st = lib.kcg_gemm_host_staged(ctypes.byref(d), a_host.data_ptr(), b_host.data_ptr(), c_host.data_ptr(),
+                                      a_dev.data_ptr(), b_dev.data_ptr(), c_dev.data_ptr(),
+                                      ws.data_ptr() if ws is not None else None, ws_bytes, chunks,
+                                      torch.cuda.current_stream(dev).cuda_stream)
+    capi.check(st, "kcg_gemm_host_staged")
+    return c_host
+
+
 def matmul_relu(a: torch.Tensor, b: torch.Tensor, **kw) -> torch.Tensor:
     """The `@fuse_matmul_relu` operator: max(0, A . B)."""
     return matmul(a, b, relu=True, **kw)

@@ -49,6 +49,20 @@ def _worker(rank, world, port, out_dir):
     got = cm.tensor.float().cpu().numpy()
     want = oracle.matmul_relu(a.float().numpy(), b.float().numpy())
     err = float(np.abs(got - want).max() / np.abs(want).max())
+    # the same all-gather through the host-buffer entry: strips computed from chunked copies
+    # must land in both ranks' copies of C and in this rank's host block
+    cm.tensor.fill_(-1.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    a_h, b_h = a[lo:hi].contiguous().pin_memory(), b.pin_memory()
+    c_h = torch.empty((hi - lo, n), dtype=torch.bfloat16).pin_memory()
+    a_d, b_d = torch.zeros_like(a_h, device=dev), torch.zeros_like(b_h, device=dev)
+    ops.matmul_host(a_h, b_h, c_h, a_d, b_d, cm.tensor[lo:hi], relu=True, peers=cm.peer_row_ptrs(lo), chunks=2)
+    dist.all_reduce(token)
+    torch.cuda.synchronize()
+    got = cm.tensor.float().cpu().numpy()
+    err = max(err, float(np.abs(got - want).max() / np.abs(want).max()))
+    err = max(err, float(np.abs(c_h.float().numpy() - want[lo:hi]).max() / np.abs(want).max()))
     status = ops.last_device_status()
     Path(out_dir, f"r{rank}.txt").write_text(f"{err} {status}")
     cm.close()
