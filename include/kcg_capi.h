@@ -108,11 +108,21 @@ typedef struct kcg_fmha_desc {
   int32_t reserved;
 } kcg_fmha_desc;
 
-/* Scratch the launch needs (bytes; may be 0). 3xTF32 GEMM: the fp32 residuals (x minus its
- * TF32 truncation) of A and B, 4*(M*K + K*N) bytes, each array rounded up to 256.
+/* Scratch the launch can use (bytes; may be 0).
+ * GEMM: (1) required for 3xTF32: the fp32 residuals (x minus its TF32 truncation) of A and B,
+ * 4*(M*K + K*N) bytes, each array rounded up to 256; (2) optional, behind (1), for launches on
+ * CTA pairs whose tile count does not fill the last wave of the persistent grid: room for the
+ * partial accumulators of the shared-K tail (the k-blocks of the left-over tiles are divided
+ * between all CTA pairs, and the partial sums meet in the workspace).  A launch given only (1),
+ * or no workspace for bf16/TF32, runs without the shared-K tail: same result up to fp32
+ * summation order, a little slower when the last wave is poorly filled.
  * FMHA with f32 inputs: bf16 copies of Q, K, V. */
 size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d);
 size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d);
+
+/* Introspection (no counterpart in the reference): how many left-over tiles the shared-K tail
+ * covers for this descriptor on a B200's 74 CTA pairs; 0 = the launch has no shared-K tail. */
+int kcg_gemm_shared_k_tiles(const kcg_gemm_desc* d);
 
 /* Replaces: launch of `<graph>::kernel0(A, B, C)` emitted by CUDAGen
  * (src/Backend/CUDA.cc:773-857) for the scheduled Matmul func, with Relu fused. */
@@ -127,7 +137,7 @@ kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* 
  * fixed array that is part of the library image, KCG_STATIC_SCRATCH_BYTES (32 MiB) on every
  * GPU that loads the library, held until the process exits.  This call performs no
  * cudaMalloc/cudaFree and calls nothing that allocates.
- *   - Limit: kcg_gemm_workspace_bytes(d) <= KCG_STATIC_SCRATCH_BYTES, i.e.
+ *   - Limit: the residual arrays must fit KCG_STATIC_SCRATCH_BYTES, i.e.
  *     4*(M*K + K*N) bytes (each term rounded up to 256) -- e.g. up to 1024 x N x 1024 with
  *     N <= 7168, or 2048 x 2048 x 2048.  Larger problems return KCG_TOO_LARGE (and say so on
  *     stderr).

@@ -34,6 +34,7 @@ KCG_ROW_MAJOR, KCG_COL_MAJOR = 0, 1
 EXPORTED_SYMBOLS = (
     "kcg_gemm_workspace_bytes",
     "kcg_fmha_workspace_bytes",
+    "kcg_gemm_shared_k_tiles",
     "kcg_gemm_launch",
     "kcg_gemm_launch_static",
     "kcg_fmha_fwd_launch",
@@ -103,6 +104,8 @@ def load() -> ctypes.CDLL:
     lib.kcg_gemm_workspace_bytes.restype = c_size_t
     lib.kcg_gemm_workspace_bytes.argtypes = [POINTER(GemmDesc)]
     lib.kcg_fmha_workspace_bytes.restype = c_size_t
+    lib.kcg_gemm_shared_k_tiles.restype = c_int
+    lib.kcg_gemm_shared_k_tiles.argtypes = [POINTER(GemmDesc)]
     lib.kcg_fmha_workspace_bytes.argtypes = [POINTER(FmhaDesc)]
     lib.kcg_gemm_launch.restype = c_int
     lib.kcg_gemm_launch.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]

@@ -124,6 +124,7 @@ extern "C" {
 
 size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d) { return gemm_workspace_impl(d); }
 size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d) { return fmha_workspace_impl(d); }
+int kcg_gemm_shared_k_tiles(const kcg_gemm_desc* d) { return gemm_shared_k_tiles_impl(d); }
 
 kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                              void* workspace, size_t workspace_bytes, void* stream) {

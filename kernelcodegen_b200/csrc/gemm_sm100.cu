@@ -48,6 +48,58 @@ struct GemmParams {
   uint32_t spin;
   int n_peers;
   void* peers[8];
+  // Shared-K tail (CTA-pair kernel): the last `sk_tiles` tiles do not fill a wave of the
+  // persistent grid, so their k-blocks, laid end to end (`sk_span` >= num_kb positions per tile;
+  // positions past num_kb are padding that makes a tile a whole number of ranges), are cut into
+  // `sk_units` ranges of `sk_share` positions, one per pair; partial accumulators meet in
+  // `sk_partial`.
+  int sk_tiles, sk_units, sk_share, sk_span, sk_maxc;
+  float* sk_partial;
+  int* sk_count;   // one arrival counter per (tile, CTA of the pair, epilogue warp); zero between launches
+};
+
+// One piece of work of a persistent CTA (pair): k-blocks [kb0, kb1) of output tile t.
+struct WorkItem {
+  int t, kb0, kb1;
+};
+
+// Walks a pair's work: its range of the shared-K tiles (which may end one tile and begin the
+// next), then whole tiles pair, pair + stride, ... below `dp_tiles`.
+struct WorkIter {
+  int t_next, stride, dp_tiles, num_kb, span, lin0, lin1;
+  __device__ __forceinline__ WorkIter(const GemmParams& p, int unit, int units, int num_tiles, int nkb)
+      : t_next(unit), stride(units), dp_tiles(num_tiles - p.sk_tiles), num_kb(nkb), span(p.sk_span), lin0(0), lin1(0) {
+    if (p.sk_tiles > 0 && unit < p.sk_units) {
+      const int total = p.sk_tiles * span;
+      lin0 = min(total, unit * p.sk_share);
+      lin1 = min(total, lin0 + p.sk_share);
+    }
+  }
+  __device__ __forceinline__ bool next(WorkItem& w) {
+    // The shared-K range comes first: adding up the partial accumulators takes a few L2 round
+    // trips, and done first it runs beside the main loop of the whole tiles that follow
+    // (the accumulators are double buffered) instead of at the very end of the kernel.
+    while (lin0 < lin1) {
+      const int ti = lin0 / span;
+      const int off = lin0 - ti * span;
+      const int end = min(span, off + (lin1 - lin0));
+      lin0 += end - off;
+      if (off < num_kb) {   // not all padding
+        w.t = dp_tiles + ti;
+        w.kb0 = off;
+        w.kb1 = min(num_kb, end);
+        return true;
+      }
+    }
+    if (t_next < dp_tiles) {
+      w.t = t_next;
+      w.kb0 = 0;
+      w.kb1 = num_kb;
+      t_next += stride;
+      return true;
+    }
+    return false;
+  }
 };
 
 template <int KIND, int BN>
@@ -67,9 +119,15 @@ struct GemmCfg {
 
 // Epilogue of one accumulator tile for one warp: TMEM rows [32 lanes] x BN columns -> ReLU ->
 // OutT -> global rows row0.. (and the same rows of every peer copy of C).
+//
+// With `sk_src` set, the tile is the sum of `sk_n` partial accumulators of this warp's slab: slot
+// `sk_own` is the one in TMEM, the others lie in global memory (slot s at sk_src + s * 32 * BN
+// floats, laid out as write_partial leaves them).  They are added in slot order, so the result
+// does not depend on which contributor happens to finish last.
 template <int BN, typename OutT>
 __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, int row0, int col0,
-                                           uint8_t* epi_stage, int lane) {
+                                           uint8_t* epi_stage, int lane, const float* sk_src = nullptr,
+                                           int sk_n = 0, int sk_own = 0) {
       // Each pass handles CW columns = 128 bytes of output per row: thread t (row t of the
       // slab) packs its part into the warp's staging slab [32 rows x 128 B] (16-byte chunks
       // XOR-swizzled by row against bank conflicts); the warp then writes the slab out with
@@ -84,7 +142,54 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
         for (int sub = 0; sub < CW / 32; ++sub) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + c0 + sub * 32, r);
-          tmem_ld_wait();
+          if (sk_src != nullptr) {
+            // the first foreign slot is fetched while the TMEM load is in flight (one L2 round trip
+            // per chunk for two contributors); any further ones one after the other
+            const float4* src = reinterpret_cast<const float4*>(sk_src) + ((c0 / 32 + sub) * 8) * 32 + lane;
+            const int f0 = sk_own == 0 ? 1 : 0;
+            float4 v0[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v0[j] = __ldcg(src + static_cast<size_t>(f0) * (8 * BN) + j * 32);
+            tmem_ld_wait();
+            float acc[32];
+            for (int sl = 0; sl < sk_n; ++sl) {
+              if (sl == sk_own) {
+                if (sl == 0) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(r[i]);
+                }
+              } else {
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  v[j] = (sl == f0) ? v0[j] : __ldcg(src + static_cast<size_t>(sl) * (8 * BN) + j * 32);
+                if (sl == 0) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    acc[4 * j] = v[j].x;
+                    acc[4 * j + 1] = v[j].y;
+                    acc[4 * j + 2] = v[j].z;
+                    acc[4 * j + 3] = v[j].w;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    acc[4 * j] += v[j].x;
+                    acc[4 * j + 1] += v[j].y;
+                    acc[4 * j + 2] += v[j].z;
+                    acc[4 * j + 3] += v[j].w;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(acc[i]);
+          } else {
+            tmem_ld_wait();
+          }
           if (p.relu) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = (r[i] & 0x80000000u) ? 0u : r[i];
@@ -144,6 +249,24 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
           __syncwarp();
         }
       }
+}
+
+// One warp's 32 x BN slab of a partial accumulator, TMEM -> global.  Float4 j of 32-column chunk
+// c of row `lane` goes to float4 index (c * 8 + j) * 32 + lane: every store instruction of the
+// warp covers 512 contiguous bytes, and the reader uses the same mapping.
+template <int BN>
+__device__ __forceinline__ void write_partial(uint32_t t_row, float* dst, int lane) {
+  float4* out = reinterpret_cast<float4*>(dst) + lane;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      __stcg(out + (c * 8 + j) * 32, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+  }
 }
 
 template <int KIND, int BN, int STAGES, bool B_KMAJOR, typename OutT>
@@ -478,12 +601,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      WorkIter it(p, pair, num_pairs, num_tiles, num_kb);
+      WorkItem w;
+      while (ok && it.next(w)) {
         int mb, nb;
-        tile_coord(t, mb, nb);
+        tile_coord(w.t, mb, nb);
         const int m0 = mb * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = nb * BN + static_cast<int>(rank) * BNL;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER, p.spin);
           if (!ok) break;
           const uint32_t full = mapa_shared(bar_full + 8 * stage, 0);   // the leader's barrier
@@ -519,7 +644,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       const uint64_t a_desc0 = make_smem_desc(base, 16, 1024);
       const uint64_t b_desc0 = make_smem_desc(base + Cfg::NOPS * A_BYTES, B_LBO, B_SBO, B_LAYOUT);
-      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++local) {
+      WorkIter it(p, pair, num_pairs, num_tiles, num_kb);
+      WorkItem w;
+      for (; ok && it.next(w); ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
         ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status,
@@ -527,7 +654,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = __all_sync(0xFFFFFFFFu, mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status,
                                                  DEV_TIMEOUT_MMA_FULL, p.spin));
           if (!ok) break;
@@ -543,7 +670,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int k = 0; k < BK / UK; ++k)
                   umma_tf32_ss_pair(d_tmem, ad0 + a_off + ((k * 32) >> 4), bd0 + b_off + ((k * B_KSTEP) >> 4),
-                                    IDESC, (kb | pass | k) ? 1u : 0u);
+                                    IDESC, ((kb - w.kb0) | pass | k) ? 1u : 0u);
               }
             } else {
 #pragma unroll
@@ -551,9 +678,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const uint64_t ad = ad0 + ((k * 32) >> 4);
                 const uint64_t bd = bd0 + ((k * B_KSTEP) >> 4);
                 if (KIND == 0)
-                  umma_bf16_ss_pair(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
+                  umma_bf16_ss_pair(d_tmem, ad, bd, IDESC, ((kb - w.kb0) | k) ? 1u : 0u);
                 else
-                  umma_tf32_ss_pair(d_tmem, ad, bd, IDESC, (kb | k) ? 1u : 0u);
+                  umma_tf32_ss_pair(d_tmem, ad, bd, IDESC, ((kb - w.kb0) | k) ? 1u : 0u);
               }
             }
             // the stage is free in both CTAs once these UMMAs have read it
@@ -582,9 +709,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t tempty_leader = mapa_shared(bar_tempty, 0);
     int local = 0;
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += num_pairs, ++local) {
+    WorkIter it(p, pair, num_pairs, num_tiles, num_kb);
+    WorkItem w;
+    for (; ok && it.next(w); ++local) {
       int mb, nb;
-      tile_coord(t, mb, nb);
+      tile_coord(w.t, mb, nb);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE, p.spin);
@@ -592,7 +721,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row0 = mb * 2 * BM + static_cast<int>(rank) * BM + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      drain_tile<BN, OutT>(p, t_row, row0, nb * BN, epi_stage, lane);
+      if (w.kb1 - w.kb0 == num_kb) {
+        drain_tile<BN, OutT>(p, t_row, row0, nb * BN, epi_stage, lane);
+      } else {
+        // Part of a tile's K range.  Every contributor leaves its partial slab in global memory and
+        // counts itself in; nobody waits: whoever finds all the others already counted adds the
+        // slabs up (in slot order) and writes the tile.
+        const int ti = w.t - (num_tiles - p.sk_tiles);
+        const int first = (ti * p.sk_span) / p.sk_share;
+        const int last = min(p.sk_units - 1, (ti * p.sk_span + num_kb - 1) / p.sk_share);
+        const int n_contrib = last - first + 1;
+        const int slab = (ti * 2 + static_cast<int>(rank)) * 4 + q;
+        float* slab_base = p.sk_partial + static_cast<size_t>(slab) * p.sk_maxc * (32 * BN);
+        write_partial<BN>(t_row, slab_base + static_cast<size_t>(pair - first) * (32 * BN), lane);
+        __syncwarp();
+        // release the warp's slab and learn how many contributors came before, in one atomic
+        int seen = 0;
+        if (lane == 0) seen = atom_add_acq_rel_gpu(p.sk_count + slab, 1);
+        seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+        if (seen == n_contrib - 1) {
+          drain_tile<BN, OutT>(p, t_row, row0, nb * BN, epi_stage, lane, slab_base, n_contrib, pair - first);
+          if (lane == 0) p.sk_count[slab] = 0;   // ready for the next launch
+        }
+      }
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + 8 * acc);
     }
@@ -639,6 +790,79 @@ __global__ void split_lo_kernel(SplitArgs a, SplitArgs b) {
 
 inline size_t pad256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
+// Arrival counters of the shared-K tail.  A launch uses one row; rows are handed out round robin,
+// so launches that overlap on one device (different streams) do not share counters unless
+// SK_ROWS of them are in flight at once.  The kernel leaves every counter it used at zero.
+constexpr int SK_ROWS = 32;
+constexpr int SK_MAX_TILES = 80;                       // tail tiles: fewer than the pairs of one wave
+constexpr int SK_ROW_INTS = SK_MAX_TILES * 8;          // tile x CTA of the pair x epilogue warp
+static __device__ int g_sk_counters[SK_ROWS * SK_ROW_INTS];
+std::atomic<unsigned> g_sk_row{0};
+
+static kcg_status_t sk_counters_ptr(int** out) {
+  static std::mutex mu;
+  static int* cache[64] = {};
+  int dev = 0;
+  KCG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KCG_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* q = nullptr;
+    KCG_CUDA_TRY(cudaGetSymbolAddress(&q, g_sk_counters));
+    if (!q) return KCG_CUDA_ERROR;
+    cache[dev] = static_cast<int*>(q);
+  }
+  *out = cache[dev];
+  return KCG_OK;
+}
+
+// Plan of the shared-K tail for `tiles` pair tiles of `num_kb` k-blocks on `pairs` CTA pairs.
+struct SkPlan {
+  int tiles = 0, units = 0, share = 0, span = 0, maxc = 0;
+  size_t bytes = 0;    // partial accumulators
+};
+inline SkPlan plan_shared_k(int tiles, int num_kb, int pairs, int bn) {
+  SkPlan pl;
+  if (pairs <= 1 || tiles % pairs == 0) return pl;
+  const int r = tiles % pairs;
+  if (r > SK_MAX_TILES) return pl;
+  constexpr int MIN_SHARE = 8;   // k-blocks: a few microseconds of tensor work per range
+  int share, span;
+  if (pairs / r >= 2) {
+    // every left-over tile is cut into g equal ranges: g contributors per tile, none shared
+    int g = std::min(pairs / r, 4);
+    while (g > 1 && ((num_kb + g - 1) / g < MIN_SHARE || (g - 1) * ((num_kb + g - 1) / g) >= num_kb)) --g;
+    if (g < 2) return pl;
+    share = (num_kb + g - 1) / g;
+    span = g * share;
+  } else {
+    // more left-over tiles than half the pairs: equal ranges of the k-blocks laid end to end; a
+    // range may end one tile and begin the next (at most 3 contributors per tile)
+    const long long total = static_cast<long long>(r) * num_kb;
+    long long sh = (total + pairs - 1) / pairs;
+    sh = std::max<long long>(sh, MIN_SHARE);
+    sh = std::max<long long>(sh, (num_kb + 1) / 2);
+    if (sh * 5 > static_cast<long long>(num_kb) * 4) return pl;   // tail less than a fifth shorter
+    share = static_cast<int>(sh);
+    span = num_kb;
+  }
+  const long long total = static_cast<long long>(r) * span;
+  const int units = static_cast<int>((total + share - 1) / share);
+  int maxc = 1;
+  for (int t = 0; t < r; ++t) {
+    const long long first = (static_cast<long long>(t) * span) / share;
+    const long long last = std::min<long long>(units - 1, (static_cast<long long>(t) * span + num_kb - 1) / share);
+    maxc = std::max(maxc, static_cast<int>(last - first + 1));
+  }
+  pl.tiles = r;
+  pl.units = units;
+  pl.share = share;
+  pl.span = span;
+  pl.maxc = maxc;
+  pl.bytes = static_cast<size_t>(r) * 8 * maxc * 32 * bn * sizeof(float);
+  return pl;
+}
+
 template <int KIND, int BN, bool B_KMAJOR, typename OutT>
 kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
                              const CUtensorMap& tB2, const GemmParams& p, int stages_req,
@@ -678,8 +902,9 @@ kcg_status_t dispatch_shape(int bn, bool b_kmajor, const CUtensorMap& tA, const 
 
 template <int KIND, int BN, bool B_KMAJOR, typename OutT>
 kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
-                                  const CUtensorMap& tB2, const GemmParams& p, int stages_req,
-                                  cudaStream_t stream) {
+                                  const CUtensorMap& tB2, const GemmParams& p_in, int stages_req,
+                                  cudaStream_t stream, void* sk_ws, size_t sk_ws_bytes) {
+  GemmParams p = p_in;
   using Cfg = PairCfg<KIND, BN>;
   constexpr int STAGES = Cfg::MAX_STAGES > 8 ? 8 : Cfg::MAX_STAGES;
   static_assert(STAGES >= 2, "need at least two pipeline stages");
@@ -704,7 +929,22 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
   int max_clusters = 0;
   KCG_CUDA_TRY(cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg));
   if (max_clusters <= 0) return KCG_UNSUPPORTED;
-  const int pairs = tiles < max_clusters ? tiles : max_clusters;
+  int pairs = tiles < max_clusters ? tiles : max_clusters;
+  // shared-K tail, when the caller's workspace has room for the partial accumulators
+  const SkPlan pl = plan_shared_k(tiles, (p.K + Cfg::BK - 1) / Cfg::BK, max_clusters, BN);
+  if (pl.tiles > 0 && sk_ws && sk_ws_bytes >= pl.bytes) {
+    int* counters = nullptr;
+    const kcg_status_t st = sk_counters_ptr(&counters);
+    if (st != KCG_OK) return st;
+    p.sk_tiles = pl.tiles;
+    p.sk_units = pl.units;
+    p.sk_share = pl.share;
+    p.sk_span = pl.span;
+    p.sk_maxc = pl.maxc;
+    p.sk_partial = static_cast<float*>(sk_ws);
+    p.sk_count = counters + (g_sk_row.fetch_add(1) % SK_ROWS) * SK_ROW_INTS;
+    pairs = tiles >= max_clusters ? max_clusters : pl.units;
+  }
   cfg.gridDim = dim3(2 * pairs);
   KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p));
   g_launches.fetch_add(1);
@@ -714,26 +954,71 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
 template <int KIND, typename OutT>
 kcg_status_t dispatch_pair_shape(int bn, bool b_kmajor, const CUtensorMap& tA, const CUtensorMap& tB,
                                  const CUtensorMap& tA2, const CUtensorMap& tB2, const GemmParams& p,
-                                 int stages, cudaStream_t s) {
+                                 int stages, cudaStream_t s, void* sk_ws, size_t sk_bytes) {
   if (bn == 256) {
-    return b_kmajor ? launch_pair_instance<KIND, 256, true, OutT>(tA, tB, tA2, tB2, p, stages, s)
-                    : launch_pair_instance<KIND, 256, false, OutT>(tA, tB, tA2, tB2, p, stages, s);
+    return b_kmajor ? launch_pair_instance<KIND, 256, true, OutT>(tA, tB, tA2, tB2, p, stages, s, sk_ws, sk_bytes)
+                    : launch_pair_instance<KIND, 256, false, OutT>(tA, tB, tA2, tB2, p, stages, s, sk_ws, sk_bytes);
   }
   if (bn == 128) {
-    return b_kmajor ? launch_pair_instance<KIND, 128, true, OutT>(tA, tB, tA2, tB2, p, stages, s)
-                    : launch_pair_instance<KIND, 128, false, OutT>(tA, tB, tA2, tB2, p, stages, s);
+    return b_kmajor ? launch_pair_instance<KIND, 128, true, OutT>(tA, tB, tA2, tB2, p, stages, s, sk_ws, sk_bytes)
+                    : launch_pair_instance<KIND, 128, false, OutT>(tA, tB, tA2, tB2, p, stages, s, sk_ws, sk_bytes);
   }
   return KCG_UNSUPPORTED;
 }
 
 }  // namespace
 
+// Kernel variant and tile width for a descriptor.  Defaults, from interleaved measurements on one
+// B200 under its 1000 W power cap:
+//  - short launches (< ~4 TFLOP of work) run faster on CTA pairs (bf16 4096^3 +8 %, 8192^3 +4 %;
+//    3xTF32 with 128-wide tiles +15..30 % on 4096x2048x1024 and 4096^3);
+//  - long launches are power-limited, and there the pair kernel sustains lower clocks
+//    (bf16 16384^3 -3.5 %, 32768^3 -19 %), so single CTAs with 256-wide tiles are used.
+static void resolve_variant(const kcg_gemm_desc* d, int* bn, bool* pair_mode) {
+  const double work = 2.0 * static_cast<double>(d->M) * static_cast<double>(d->N) * static_cast<double>(d->K);
+  const bool small_job = work < 4e12;
+  *bn = d->tile_n;
+  if (*bn == 0) *bn = (d->precision == KCG_PREC_3XTF32 && small_job) ? 128 : 256;
+  *pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM && small_job);
+}
+
+// Tail tiles the shared-K plan covers for this descriptor on 74 CTA pairs (0 = no shared-K tail).
+int gemm_shared_k_tiles_impl(const kcg_gemm_desc* d) {
+  if (!d || d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
+  if (d->M > 0x7FFFFFFF || d->N > 0x7FFFFFFF || d->K > 0x7FFFFFFF) return 0;
+  int bn = 0;
+  bool pair_mode = false;
+  resolve_variant(d, &bn, &pair_mode);
+  if (!pair_mode || (bn != 128 && bn != 256)) return 0;
+  const int bk = d->precision == KCG_PREC_BF16 ? 64 : 32;
+  const long long tiles = ((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn);
+  if (tiles > 0x7FFFFFFF) return 0;
+  return plan_shared_k(static_cast<int>(tiles), static_cast<int>((d->K + bk - 1) / bk), 74, bn).tiles;
+}
+
+// bytes of the 3xTF32 residual arrays at the head of the workspace
+static size_t gemm_lo_bytes(const kcg_gemm_desc* d) {
+  if (d->precision != KCG_PREC_3XTF32) return 0;
+  return pad256(static_cast<size_t>(d->M) * d->K * 4) + pad256(static_cast<size_t>(d->K) * d->N * 4);
+}
+
 size_t gemm_workspace_impl(const kcg_gemm_desc* d) {
-  if (!d || d->precision != KCG_PREC_3XTF32) return 0;
+  if (!d) return 0;
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
-  const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
-  const size_t b = pad256(static_cast<size_t>(d->K) * d->N * 4);
-  return a + b;
+  if (d->M > 0x7FFFFFFF || d->N > 0x7FFFFFFF || d->K > 0x7FFFFFFF) return 0;
+  size_t need = gemm_lo_bytes(d);
+  // room for the partial accumulators of the shared-K tail, planned for the 74 CTA pairs of a
+  // B200 (the launch plans again for the device it runs on and goes without if this is too small)
+  int bn = 0;
+  bool pair_mode = false;
+  resolve_variant(d, &bn, &pair_mode);
+  if (pair_mode && (bn == 128 || bn == 256)) {
+    const int bk = d->precision == KCG_PREC_BF16 ? 64 : 32;
+    const long long tiles = ((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn);
+    if (tiles <= 0x7FFFFFFF)
+      need += plan_shared_k(static_cast<int>(tiles), static_cast<int>((d->K + bk - 1) / bk), 74, bn).bytes;
+  }
+  return need;
 }
 
 kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
@@ -763,18 +1048,11 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   if ((d->lda * es) % 16 || (d->ldb * es) % 16 || (d->ldc * os) % 16) return KCG_BAD_ALIGN;
   for (int i = 0; i < d->n_peers; ++i)
     if (!d->peer_c[i] || !aligned16(d->peer_c[i])) return KCG_BAD_ALIGN;
-  // Defaults, from interleaved measurements on one B200 under its 1000 W power cap:
-  //  - short launches (< ~4 TFLOP of work) run faster on CTA pairs (bf16 4096^3 +8 %, 8192^3 +4 %;
-  //    3xTF32 with 128-wide tiles +15..30 % on 4096x2048x1024 and 4096^3);
-  //  - long launches are power-limited, and there the pair kernel sustains lower clocks
-  //    (bf16 16384^3 -3.5 %, 32768^3 -19 %), so single CTAs with 256-wide tiles are used.
-  const double work = 2.0 * static_cast<double>(d->M) * static_cast<double>(d->N) * static_cast<double>(d->K);
-  const bool small_job = work < 4e12;
-  int bn = d->tile_n;
-  if (bn == 0) bn = (kind == 2 && small_job) ? 128 : 256;
+  int bn = 0;
+  bool pair_mode = false;
+  resolve_variant(d, &bn, &pair_mode);
   if (bn != 128 && bn != 256) return KCG_UNSUPPORTED;
   if (d->cta_group != 0 && d->cta_group != 1 && d->cta_group != 2) return KCG_UNSUPPORTED;
-  const bool pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM && small_job);
 
   const void* pa = A;
   const void* pb = B;
@@ -783,7 +1061,7 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   long long lda = d->lda, ldb = d->ldb;
   long long lda2 = d->lda, ldb2 = d->ldb;  // leading dimensions of the residual arrays
   if (kind == 2) {
-    const size_t need = gemm_workspace_impl(d);
+    const size_t need = gemm_lo_bytes(d);
     if (!ws || ws_bytes < need || !aligned16(ws)) return KCG_BAD_WORKSPACE;
     if ((d->K % 4) || (d->N % 4)) return KCG_BAD_ALIGN;
     const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
@@ -859,15 +1137,24 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   p.spin = spin ? spin : KCG_SPIN_LIMIT;
   p.n_peers = d->n_peers;
   for (int i = 0; i < 8; ++i) p.peers[i] = i < d->n_peers ? d->peer_c[i] : nullptr;
+  p.sk_tiles = p.sk_units = p.sk_share = p.sk_span = p.sk_maxc = 0;
+  p.sk_partial = nullptr;
+  p.sk_count = nullptr;
 
   if (pair_mode) {
+    // what follows the residual arrays in the workspace is free for the shared-K tail
+    const size_t lo_bytes = gemm_lo_bytes(d);
+    void* sk_ws = (ws && aligned16(ws) && ws_bytes > lo_bytes) ? static_cast<uint8_t*>(ws) + lo_bytes : nullptr;
+    const size_t sk_bytes = sk_ws ? ws_bytes - lo_bytes : 0;
     if (kind == 0) {
       if (d->dtype_out == KCG_BF16)
-        return dispatch_pair_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
-      return dispatch_pair_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+        return dispatch_pair_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws,
+                                                     sk_bytes);
+      return dispatch_pair_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
     }
-    if (kind == 1) return dispatch_pair_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
-    return dispatch_pair_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+    if (kind == 1)
+      return dispatch_pair_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
+    return dispatch_pair_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
   }
   if (kind == 0) {
     if (d->dtype_out == KCG_BF16)
@@ -903,7 +1190,7 @@ kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, cons
   if (!d) return KCG_BAD_ARGUMENT;
   if (d->precision != KCG_PREC_3XTF32) return KCG_UNSUPPORTED;
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
-  const size_t need = gemm_workspace_impl(d);
+  const size_t need = gemm_lo_bytes(d);
   if (need > STATIC_SCRATCH_BYTES) {
     std::fprintf(stderr,
                  "kcg: kcg_gemm_launch_static: %lld x %lld x %lld needs %zu bytes of scratch, the "
@@ -917,7 +1204,9 @@ kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, cons
   if (st != KCG_OK) return st;
   // The split pass overwrites every byte of scratch the GEMM then reads, so nothing left by an
   // earlier call is ever consumed and nothing has to be cleared.
-  return gemm_launch_impl(d, A, B, C, scratch, STATIC_SCRATCH_BYTES, stream);
+  // Exactly the residual arrays are handed on, so the shared-K tail (which would use the rest of
+  // the scratch for partial accumulators) stays off on this entry.
+  return gemm_launch_impl(d, A, B, C, scratch, need, stream);
 }
 
 }  // namespace kcg

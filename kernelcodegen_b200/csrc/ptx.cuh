@@ -96,6 +96,14 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// Atomic add that releases this thread's (and, after a __syncwarp, its warp's) earlier writes
+// and acquires what earlier adders released.
+__device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+  return old;
+}
+
 // ---- TMA loads (per-CTA, no multicast) -------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int x, int y) {

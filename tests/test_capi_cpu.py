@@ -51,6 +51,21 @@ def test_workspace_sizes(native_lib):
     assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 2 * 256 * 256 * 4
     d = _gemm_desc(prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)
     assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 0
+    # shared-K tail: 4096x2048x1024 fp32 makes 256 pair tiles of 256x128 = 3 waves of 74 pairs + 34
+    d = _gemm_desc(4096, 2048, 1024)
+    assert native_lib.kcg_gemm_shared_k_tiles(ctypes.byref(d)) == 34
+    lo = 4 * (4096 * 1024 + 1024 * 2048)
+    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == lo + 34 * 8 * 2 * 32 * 128 * 4
+    d.cta_group = 1                       # single CTAs: no tail sharing, residual arrays only
+    assert native_lib.kcg_gemm_shared_k_tiles(ctypes.byref(d)) == 0
+    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == lo
+    d = _gemm_desc(1024, 1024, 1024)      # 32 pair tiles on 74 pairs: all of them share K
+    assert native_lib.kcg_gemm_shared_k_tiles(ctypes.byref(d)) == 32
+    d = _gemm_desc(32768, 32768, 32768, prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)   # long launch: single CTAs
+    assert native_lib.kcg_gemm_shared_k_tiles(ctypes.byref(d)) == 0
+    assert native_lib.kcg_gemm_workspace_bytes(ctypes.byref(d)) == 0
+    d = _gemm_desc(4096, 4096, 4096, prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)      # 256 tiles of 256x256
+    assert native_lib.kcg_gemm_shared_k_tiles(ctypes.byref(d)) == 34
     f = capi.FmhaDesc()
     f.B, f.H, f.Sq, f.Skv, f.D = 2, 3, 128, 256, 64
     f.dtype_in = capi.KCG_F32

@@ -104,7 +104,10 @@ def test_optimize_fuses_relu_and_dispatches(stages):
     code = stages["codegen_matmul_relu"]
     assert "namespace matmul_demo" in code and "kernel0(const float* A, const float* B, float* C" in code
     assert "d.M = 4096; d.N = 2048; d.K = 1024;" in code and "d.epilogue = 1;" in code and "d.precision = 0;" in code
-    assert "plans 1 status 0 epilogue 1 buffers 012 ws 25165824" in code
+    # workspace: the 3xTF32 residual arrays (4 * (M*K + K*N) bytes) plus room for the partial
+    # accumulators of the shared-K tail (34 left-over pair tiles, 2 contributors each)
+    ws = 4 * (4096 * 1024 + 1024 * 2048) + 34 * 8 * 2 * 32 * 128 * 4
+    assert f"plans 1 status 0 epilogue 1 buffers 012 ws {ws}" in code
 
 
 def test_fmha_chain_is_fused(stages):
