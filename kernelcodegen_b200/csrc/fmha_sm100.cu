@@ -157,6 +157,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     reg_dealloc_56();
     if (warp == 0 && lane == 0 && n_kv > 0) {
       // ------------------------------- TMA producer -----------------------------------------
+      // fp32 inputs: the bf16 copies come from the launch just before this one (no-op otherwise)
+      griddep_wait();
 #pragma unroll
       for (int t = 0; t < QTILES; ++t) {
         if (n_kv_t[t] == 0) continue;
@@ -453,6 +455,7 @@ struct CastArgs {
   long long n4[3];
 };
 __global__ void f32_to_bf16_kernel(CastArgs a) {
+  griddep_launch_dependents();   // the attention kernel may move in as SMs become free
   const long long total = a.n4[0] + a.n4[1] + a.n4[2];
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -475,16 +478,25 @@ inline size_t pad256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 template <int D>
 kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const FmhaParams& p, int bh, cudaStream_t stream) {
+                         const FmhaParams& p, int bh, cudaStream_t stream, bool after_cast) {
   using Cfg = FmhaCfg<D>;
   static_assert(Cfg::SMEM_TOTAL <= 232448, "shared memory budget");
   auto kern = fmha_fwd_kernel<D>;
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::SMEM_TOTAL));
   dim3 grid((p.Sq + QTILES * BQ - 1) / (QTILES * BQ), bh);
-  kern<<<grid, FM_THREADS, Cfg::SMEM_TOTAL, stream>>>(tq, tk, tv, p);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(FM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_TOTAL;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = after_cast ? 1 : 0;
+  KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, p));
   g_launches.fetch_add(1);
-  KCG_CUDA_TRY(cudaGetLastError());
   return KCG_OK;
 }
 
@@ -568,8 +580,8 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
   if (st != KCG_OK) return st;
   const uint32_t spin = g_spin_limit.load();
   p.spin = spin ? spin : KCG_SPIN_LIMIT;
-  if (d->D == 64) return launch_fmha<64>(tq, tk, tv, p, bh, stream);
-  return launch_fmha<128>(tq, tk, tv, p, bh, stream);
+  if (d->D == 64) return launch_fmha<64>(tq, tk, tv, p, bh, stream, d->dtype_in == KCG_F32);
+  return launch_fmha<128>(tq, tk, tv, p, bh, stream, d->dtype_in == KCG_F32);
 }
 
 }  // namespace kcg

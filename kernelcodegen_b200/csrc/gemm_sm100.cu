@@ -353,6 +353,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // the residual arrays come from the launch just before this one; everything above ran
+      // beside its tail (programmatic dependent launch)
+      if (KIND == 2) griddep_wait();
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mb, nb;
         tile_coord(t, mb, nb);
@@ -601,6 +604,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (KIND == 2) griddep_wait();   // the residual arrays come from the launch just before
       WorkIter it(p, pair, num_pairs, num_tiles, num_kb);
       WorkItem w;
       while (ok && it.next(w)) {
@@ -770,6 +774,7 @@ struct SplitArgs {
   long long ld;
 };
 __global__ void split_lo_kernel(SplitArgs a, SplitArgs b) {
+  griddep_launch_dependents();   // the GEMM may move in and set itself up while this runs
   const long long na = a.rows * a.cols4, nb = b.rows * b.cols4;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < na + nb;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -878,9 +883,18 @@ kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const
   const int sms = device_sm_count();
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(tA, tB, tA2, tB2, p);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = (KIND == 2) ? 1 : 0;   // 3xTF32: overlap the set-up with the residual pass before it
+  KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p));
   g_launches.fetch_add(1);
-  KCG_CUDA_TRY(cudaGetLastError());
   return KCG_OK;
 }
 
@@ -915,11 +929,13 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(GEMM_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -946,6 +962,7 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
     pairs = tiles >= max_clusters ? max_clusters : pl.units;
   }
   cfg.gridDim = dim3(2 * pairs);
+  cfg.numAttrs = (KIND == 2) ? 2 : 1;   // 3xTF32: overlap the set-up with the residual pass before it
   KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p));
   g_launches.fetch_add(1);
   return KCG_OK;

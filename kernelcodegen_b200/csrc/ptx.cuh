@@ -96,6 +96,14 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may become resident while the kernel before it in the stream is still running;
+// griddep_wait() blocks until that kernel has completed and its writes are visible (no-op
+// without the attribute).  griddep_launch_dependents() in the earlier kernel allows the next
+// one to be scheduled as soon as every CTA has passed it.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Atomic add that releases this thread's (and, after a __syncwarp, its warp's) earlier writes
 // and acquires what earlier adders released.
 __device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
