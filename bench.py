@@ -235,8 +235,8 @@ def flush_l2(torch, buf):
 
 
 def time_flushed(fn, iters, torch, flush_buf):
-    """Per-launch timing with an L2 flush (a write larger than L2) between timed launches."""
-    total = 0.0
+    """Per-launch time (median) with an L2 flush (a write larger than L2) between timed launches."""
+    times = []
     for _ in range(iters):
         flush_l2(torch, flush_buf)
         e0 = torch.cuda.Event(enable_timing=True)
@@ -245,8 +245,9 @@ def time_flushed(fn, iters, torch, flush_buf):
         fn()
         e1.record()
         torch.cuda.synchronize()
-        total += e0.elapsed_time(e1)
-    return total / iters
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]   # median: single launches of tens of microseconds see outliers
 
 
 def measure_tf32_peak(torch, dev):
@@ -328,6 +329,17 @@ def others_single_gpu(torch, dev, peaks, ops):
                 "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                              "frac": fl / ms / 1e9 / peaks["bf16_tflops"]}})
     res.append(fmha_long(torch, dev, peaks, ops, 0, 256))
+    del qkv, o
+    # Transpose (HBM-bound): 8192 x 8192 fp32, 256 MiB in + 256 MiB out, larger than L2
+    x = torch.randn((8192, 8192), device=dev)
+    for _ in range(3):
+        y = ops.transpose(x)
+    ms = time_steps(lambda: ops.transpose(x), 10, 3, torch, None) / 10
+    nbytes = 2.0 * x.numel() * 4
+    res.append({"workload": "Transpose 8192x8192 fp32 (read once, write once)", "gbs": nbytes / ms / 1e6, "ms": ms,
+                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"]}})
+    del x, y
     return res, tf32_peak
 
 
@@ -342,12 +354,15 @@ def fmha_long(torch, dev, peaks, ops, bh_lo, bh_hi, dist=None, steps=5):
     o = torch.empty_like(qkv[0])
     scale = 128 ** -0.5
     fn = lambda: ops.fmha(qkv[0], qkv[1], qkv[2], scale=scale, causal=True, out=o)
-    ms = time_steps(fn, steps, 3, torch, dist) / steps
+    # three batches of `steps` launches; the median batch is reported and all three are listed, so
+    # a transient clock dip on a shared, power-capped box shows as such
+    batches = sorted(time_steps(fn, steps, 3 if i == 0 else 0, torch, dist) / steps for i in range(3))
+    ms = batches[1]
     fl = 2.0 * 256 * 8192 * 8192 * 128  # whole job: causal = half of 4*B*H*S^2*D
     world = dist.get_world_size() if dist is not None else 1
     peak = peaks["bf16_tflops"] * world
     return {"workload": f"FMHA bf16 causal B8 H32 S8192 D128, batch*head sharded x{world}, no collective",
-            "tflops": fl / ms / 1e9, "ms": ms,
+            "tflops": fl / ms / 1e9, "ms": ms, "ms_batches": batches,
             "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
                          "frac": fl / ms / 1e9 / peak}}
 

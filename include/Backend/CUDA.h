@@ -7,7 +7,7 @@
 // returns a small launcher translation unit -- `namespace <graph> { kernel0(...) }` as before,
 // but the body fills a descriptor and calls kcg_gemm_launch / kcg_fmha_fwd_launch -- so that
 // `save()` still writes something a harness can compile.  `launchModule` does the same calls
-// directly.  BatchedMatmul and Softmax functions that are not part of an attention chain are
+// directly.  BatchedMatmul, Softmax and Transpose functions that are not part of an attention chain are
 // dispatched as they stand to the batched GEMM and the row-softmax kernel.  There is
 // deliberately no generic affine->CUDA emitter: any other unscheduled function yields
 // KCG_UNSUPPORTED, never a fallback kernel.
@@ -23,16 +23,18 @@ namespace KernelCodeGen {
 
 // One kernel launch derived from a `func.call` of a function with func.state = "gpu".
 struct LaunchPlan {
-  enum class Kind { Gemm, Fmha, BatchedGemm, Softmax } kind = Kind::Gemm;
+  enum class Kind { Gemm, Fmha, BatchedGemm, Softmax, Transpose } kind = Kind::Gemm;
   std::string function;            // callee symbol
   kcg_gemm_desc gemm{};
   kcg_fmha_desc fmha{};
   // BatchedGemm: `gemm` describes one product; batch count and element strides between products.
   int64_t batch = 1, strideA = 0, strideB = 0, strideC = 0;
-  // Softmax: [rows, cols] fp32, in place on its single buffer.
+  // Softmax: [rows, cols] fp32, in place on its single buffer.  Transpose: `batch` matrices of
+  // [rows, cols] elements of `elem_dtype`, buffers (X, Y).
   int64_t rows = 0, cols = 0;
+  int elem_dtype = KCG_F32;
   // Position (among the module-level memref.alloc ops, in program order) of each pointer
-  // argument, in the kernel's argument order: (A, B, C), (Q, K, V, O) or (X) for Softmax.
+  // argument, in the kernel's argument order: (A, B, C), (Q, K, V, O), (X) for Softmax or (X, Y) for Transpose.
   std::vector<int> buffers;
   kcg_status_t status = KCG_OK;    // KCG_UNSUPPORTED when the schedule has no kernel
   std::string why;

@@ -92,8 +92,10 @@ struct Softmax : Operator<Softmax> {
                            MemorySpace ms = MemorySpace::global, const std::string& dtype = {""});
 };
 
-// Declared by the reference with an empty body (src/Frontend/Operators.cc:422-423); here it
-// returns its input unchanged as well.
+// out[..., j, i] = in[..., i, j] into a new global PlaceHolder.  The reference declares this
+// operator (include/Frontend/Operators.h:100-102) with an empty body
+// (src/Frontend/Operators.cc:422-423); here it builds the copy nest, and the Backend dispatches
+// it to the tiled transpose kernel.
 struct Transpose : Operator<Transpose> {
   static mlir::Value build(ComputeDAG* graph, mlir::Value input);
 };

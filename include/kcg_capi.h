@@ -165,6 +165,12 @@ kcg_status_t kcg_fmha_fwd_launch(const kcg_fmha_desc* d, const void* Q, const vo
  * where Softmax is not part of an attention chain (there it is fused into the FMHA kernel). */
 kcg_status_t kcg_softmax_launch(int64_t rows, int64_t cols, const void* x, void* y, void* stream);
 
+/* The reference's Transpose operator (include/Frontend/Operators.h:100-102; its build has no body,
+ * src/Frontend/Operators.cc:422-423): y[b, j, i] = x[b, i, j] for `batch` contiguous row-major
+ * [rows, cols] matrices of KCG_F32 or KCG_BF16 elements; out of place (x != y). */
+kcg_status_t kcg_transpose_launch(int64_t batch, int64_t rows, int64_t cols, int32_t dtype, const void* x, void* y,
+                                  void* stream);
+
 /* The reference's BatchedMatmul operator on its own (src/Frontend/Operators.cc:253-420): `batch`
  * independent products described by `d`, operand i at base + i * stride (strides in elements;
  * 0 broadcasts an operand).  Layout::colMajor B = d->b_layout KCG_COL_MAJOR.  One GEMM launch per

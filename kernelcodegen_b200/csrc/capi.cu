@@ -141,6 +141,11 @@ kcg_status_t kcg_softmax_launch(int64_t rows, int64_t cols, const void* x, void*
   return softmax_launch_impl(rows, cols, x, y, static_cast<cudaStream_t>(stream));
 }
 
+kcg_status_t kcg_transpose_launch(int64_t batch, int64_t rows, int64_t cols, int32_t dtype, const void* x, void* y,
+                                  void* stream) {
+  return transpose_launch_impl(batch, rows, cols, dtype, x, y, static_cast<cudaStream_t>(stream));
+}
+
 kcg_status_t kcg_batched_gemm_launch(const kcg_gemm_desc* d, int64_t batch, int64_t stride_a, int64_t stride_b,
                                      int64_t stride_c, const void* A, const void* B, void* C, void* workspace,
                                      size_t workspace_bytes, void* stream) {

@@ -40,6 +40,8 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
                               void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t gemm_workspace_impl(const kcg_gemm_desc* d);
 int gemm_shared_k_tiles_impl(const kcg_gemm_desc* d);
+kcg_status_t transpose_launch_impl(int64_t batch, int64_t rows, int64_t cols, int dtype, const void* x, void* y,
+                                   cudaStream_t stream);
 kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                                      cudaStream_t stream);
 kcg_status_t gemm_host_staged_impl(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC, void* dA,

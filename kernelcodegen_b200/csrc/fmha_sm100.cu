@@ -51,6 +51,7 @@ struct FmhaParams {
   float scale_log2;  // scale * log2(e)
   int* status;
   uint32_t spin;
+  int after_cast;    // the inputs come from the cast launch just before (programmatic dependent launch)
 };
 
 template <int D>
@@ -158,7 +159,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (warp == 0 && lane == 0 && n_kv > 0) {
       // ------------------------------- TMA producer -----------------------------------------
       // fp32 inputs: the bf16 copies come from the launch just before this one (no-op otherwise)
-      griddep_wait();
+      if (p.after_cast) griddep_wait();
 #pragma unroll
       for (int t = 0; t < QTILES; ++t) {
         if (n_kv_t[t] == 0) continue;
@@ -495,7 +496,9 @@ kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = after_cast ? 1 : 0;
-  KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, p));
+  FmhaParams pp = p;
+  pp.after_cast = after_cast ? 1 : 0;
+  KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, pp));
   g_launches.fetch_add(1);
   return KCG_OK;
 }

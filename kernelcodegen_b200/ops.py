@@ -202,6 +202,24 @@ def softmax(x: torch.Tensor, *, inplace: bool = False) -> torch.Tensor:
     return y
 
 
+def transpose(x: torch.Tensor) -> torch.Tensor:
+    """y[..., j, i] = x[..., i, j] as a new contiguous tensor (the reference's Transpose operator,
+    which it declares without a body); leading dimensions are batch dimensions."""
+    dev = _require_cuda(x)
+    if x.dim() < 2 or not x.is_contiguous():
+        raise ValueError("transpose takes a contiguous tensor of at least 2 dimensions")
+    rows, cols = x.shape[-2:]
+    batch = x.numel() // max(1, rows * cols)
+    y = torch.empty(x.shape[:-2] + (cols, rows), dtype=x.dtype, device=dev)
+    if x.numel() == 0:
+        return y
+    with torch.cuda.device(dev):
+        st = capi.load().kcg_transpose_launch(batch, rows, cols, _dtype_code(x.dtype), x.data_ptr(), y.data_ptr(),
+                                              torch.cuda.current_stream(dev).cuda_stream)
+    capi.check(st, "kcg_transpose_launch")
+    return y
+
+
 def batched_matmul(a: torch.Tensor, b: torch.Tensor, *, b_col_major: bool = False, precision: Optional[str] = None,
                    relu: bool = False) -> torch.Tensor:
     """C[..., m, n] = A[..., m, k] . B[..., k, n]  (B[..., n, k] when `b_col_major`): the

@@ -113,6 +113,13 @@ def batched_matmul(a, b, b_col_major: bool = False) -> np.ndarray:
     return c
 
 
+def transpose(x) -> np.ndarray:
+    """out[..., j, i] = in[..., i, j], copied.  The reference declares this operator
+    (include/Frontend/Operators.h:100-102) without a body (src/Frontend/Operators.cc:422-423);
+    the definition is the index swap its name states."""
+    return np.ascontiguousarray(np.swapaxes(np.asarray(x), -1, -2))
+
+
 def softmax(x) -> np.ndarray:
     y = _f32(x).copy()
     cols = y.shape[-1]

@@ -66,6 +66,24 @@ std::vector<LaunchPlan> planLaunches(mlir::ModuleOp& module) {
     const std::string kind = callee->getStringAttr("kcg.op");
     const bool is_bmm = callee->name.rfind("BatchMatmul_", 0) == 0 && op->operands.size() == 3;
     const bool is_softmax = callee->name.rfind("Softmax_", 0) == 0 && op->operands.size() == 1;
+    const bool is_transpose = callee->name.rfind("Transpose_", 0) == 0 && op->operands.size() == 2;
+    if (kind.empty() && is_transpose) {
+      for (auto v : op->operands) p.buffers.push_back(allocIndex(module, underlyingBuffer(module, v)));
+      const auto t0 = op->operands[0].getType();
+      p.kind = LaunchPlan::Kind::Transpose;
+      const size_t r = t0.shape.size();
+      p.rows = t0.shape[r - 2];
+      p.cols = t0.shape[r - 1];
+      p.batch = 1;
+      for (size_t i = 0; i + 2 < r; ++i) p.batch *= t0.shape[i];
+      p.elem_dtype = dtypeCode(kcgir::scalarName(t0.elem));
+      if (p.elem_dtype < 0) {
+        p.status = KCG_UNSUPPORTED;
+        p.why = "element type has no kernel (float32 and bfloat16 do)";
+      }
+      plans.push_back(p);
+      continue;
+    }
     if (kind.empty() && (is_bmm || is_softmax)) {
       // library operators: dispatched from the naive nest as it stands
       for (auto v : op->operands) p.buffers.push_back(allocIndex(module, underlyingBuffer(module, v)));
@@ -205,6 +223,9 @@ kcg_status_t launchModule(mlir::ModuleOp& module, const std::vector<void*>& buff
     } else if (p.kind == LaunchPlan::Kind::Softmax) {
       if (ptr.size() != 1) return KCG_BAD_ARGUMENT;
       st = kcg_softmax_launch(p.rows, p.cols, ptr[0], ptr[0], stream);
+    } else if (p.kind == LaunchPlan::Kind::Transpose) {
+      if (ptr.size() != 2) return KCG_BAD_ARGUMENT;
+      st = kcg_transpose_launch(p.batch, p.rows, p.cols, p.elem_dtype, ptr[0], ptr[1], stream);
     } else {
       if (ptr.size() != 4) return KCG_BAD_ARGUMENT;
       st = kcg_fmha_fwd_launch(&p.fmha, ptr[0], ptr[1], ptr[2], ptr[3], workspace, wsBytes, stream);
@@ -246,6 +267,15 @@ std::string CUDAGen(mlir::ModuleOp& module) {
     if (p.kind == LaunchPlan::Kind::Softmax) {
       os << "inline kcg_status_t kernel" << kid << "(float* X, void*, size_t, cudaStream_t stream) {\n"
          << "  return kcg_softmax_launch(" << p.rows << ", " << p.cols << ", X, X, stream);\n}\n";
+      ++kid;
+      continue;
+    }
+    if (p.kind == LaunchPlan::Kind::Transpose) {
+      const char* ct = p.elem_dtype == KCG_BF16 ? "void" : "float";
+      os << "inline kcg_status_t kernel" << kid << "(const " << ct << "* X, " << ct
+         << "* Y, void*, size_t, cudaStream_t stream) {\n"
+         << "  return kcg_transpose_launch(" << p.batch << ", " << p.rows << ", " << p.cols << ", " << p.elem_dtype
+         << ", X, Y, stream);\n}\n";
       ++kid;
       continue;
     }

@@ -276,6 +276,43 @@ mlir::Value Softmax::build(ComputeDAG* graph, mlir::Value input, int axis, Memor
   return builder.createCall(funcOp, {input}).getResult(0);
 }
 
-mlir::Value Transpose::build(ComputeDAG*, mlir::Value input) { return input; }
+mlir::Value Transpose::build(ComputeDAG* graph, mlir::Value input) {
+  auto& builder = graph->builder;
+  if (!input || !input.getType().isMemRef()) {
+    std::cerr << "Type of input of Transpose is not Memref.\n";
+    return nullptr;
+  }
+  const auto type = input.getType();
+  const int totalDims = static_cast<int>(type.shape.size());
+  if (totalDims < 2) {
+    std::cerr << "Transpose needs at least 2 dim but got " << totalDims << "\n";
+    return nullptr;
+  }
+  std::vector<int64_t> shapeOut = type.shape;
+  std::swap(shapeOut[totalDims - 2], shapeOut[totalDims - 1]);
+  const std::string dtype = toStr(type);
+  mlir::Value out = graph->create<PlaceHolder>(shapeOut, dtype);
+  const auto typeOut = out.getType();
+  std::string funcName = "Transpose";
+  for (auto dim : type.shape) funcName += "_" + std::to_string(dim);
+
+  auto ip = builder.saveInsertionPoint();
+  auto funcOp = buildFuction(graph->module, builder, funcName, {type, typeOut}, {typeOut});
+  if (!hasBody(funcOp)) {
+    builder.setInsertionPointToStart(funcOp.getBody());
+    const mlir::Value x = funcOp.getArgument(0), y = funcOp.getArgument(1);
+    std::vector<int64_t> zeros(totalDims, 0), ones(totalDims, 1);
+    builder.buildAffineLoopNest(zeros, type.shape, ones, [&](mlir::OpBuilder& nb, const std::vector<mlir::Value>& ivs) {
+      std::vector<IndexExpr> src(ivs.begin(), ivs.end()), dst(ivs.begin(), ivs.end());
+      std::swap(dst[totalDims - 2], dst[totalDims - 1]);
+      nb.createStore(nb.createLoad(x, src), y, dst);
+    });
+    builder.setInsertionPointToEnd(funcOp.getBody());
+    builder.createReturn({y});
+    funcOp->setAttr("func.state", std::string("cpu"));
+  }
+  builder.restoreInsertionPoint(ip);
+  return builder.createCall(funcOp, {input, out}).getResult(0);
+}
 
 }  // namespace KernelCodeGen

@@ -119,6 +119,21 @@ int main() {
     std::cout << "=== codegen_standalone\n" << generator.codegen(module);
   }
 
+  // ---- Transpose: a copy nest, dispatched to the tiled transpose kernel ---------------------------
+  {
+    auto graph = generator.createGraph("transpose_demo");
+    auto X = graph.create<PlaceHolder>(std::vector<int64_t>{6, 300, 520}, std::string{"float32"});
+    auto Y = graph.create<Transpose>(X);
+    (void)Y;
+    auto module = generator.optimize(graph);
+    stage("transpose", module);
+    auto plans = planLaunches(module);
+    std::cout << "plans " << plans.size() << " kind " << static_cast<int>(plans[0].kind) << " status " << plans[0].status
+              << " batch " << plans[0].batch << " rows " << plans[0].rows << " cols " << plans[0].cols << " buffers "
+              << plans[0].buffers[0] << plans[0].buffers[1] << "\n";
+    std::cout << "=== codegen_transpose\n" << generator.codegen(module);
+  }
+
   // ---- error behaviour -------------------------------------------------------------------------
   {
     auto graph = generator.createGraph("errors");

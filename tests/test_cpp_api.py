@@ -132,6 +132,13 @@ def test_standalone_batched_matmul_and_softmax_are_dispatched(stages):
     assert "kcg_batched_gemm_launch(&d, 3, 16384, 8192, 32768" in code and "kcg_softmax_launch(35, 300, X, X, stream)" in code
 
 
+def test_transpose_builds_a_copy_nest_and_is_dispatched(stages):
+    t = stages["transpose"]
+    assert "Transpose_6_300_520" in t and "memref<6x520x300xf32" in t
+    assert "plans 1 kind 4 status 0 batch 6 rows 300 cols 520 buffers 01" in t
+    assert "kcg_transpose_launch(6, 300, 520, 0, X, Y, stream)" in stages["codegen_transpose"]
+
+
 def test_error_behaviour(stages):
     t = stages["errors"]
     assert "mismatch_is_null 1" in t and "bad_dtype_is_null 1" in t

@@ -99,3 +99,13 @@ def test_fmha_rows_without_visible_keys_are_zero():
     o = oracle.fmha(q, k, v, causal=True)
     assert np.array_equal(o[0, 0, :2], np.zeros((2, 8), dtype=np.float32))
     assert np.isfinite(o).all()
+
+
+def test_transpose_swaps_the_last_two_axes():
+    x = np.arange(2 * 3 * 5, dtype=np.float32).reshape(2, 3, 5)
+    y = oracle.transpose(x)
+    assert y.shape == (2, 5, 3) and y.flags["C_CONTIGUOUS"]
+    for b in range(2):
+        for i in range(3):
+            for j in range(5):
+                assert y[b, j, i] == x[b, i, j]

@@ -66,3 +66,20 @@ def test_unfused_attention_graph_equals_fused_kernel(cuda_device):
     want = oracle.fmha(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
     assert rel_err(o_graph.cpu().numpy(), want) <= 1e-4          # fp32-contract operators
     assert rel_err(o_fused.cpu().numpy(), o_graph.cpu().numpy()) <= 2e-2
+
+
+@pytest.mark.parametrize("shape", [(64, 64), (4096, 1024), (3, 300, 520), (2, 5, 130, 66), (1, 7), (129, 1), (1000, 1002)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_transpose_is_exact(cuda_device, shape, dtype):
+    """Moves bits only: the result must equal the index-swapped input exactly (vector path for
+    multiples of 4, element-wise path for ragged tiles and odd shapes)."""
+    from kernelcodegen_b200 import ops
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g).to(dtype)
+    got = ops.transpose(x.to(cuda_device))
+    want = oracle.transpose(x.float().numpy())
+    assert got.shape == want.shape and got.is_contiguous()
+    assert np.array_equal(got.float().cpu().numpy(), want)
+    # twice is the identity
+    assert torch.equal(ops.transpose(got).cpu(), x)
+    assert ops.last_device_status() == 0
