@@ -97,7 +97,9 @@ kcg_status_t launch_transpose(int64_t batch, int64_t rows, int64_t cols, const v
   constexpr int smem = TT * (TT + 4 / static_cast<int>(sizeof(T))) * static_cast<int>(sizeof(T));
   auto kern = transpose_kernel<T, TT>;
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  const int per_sm = 200 * 1024 / smem < 8 ? 200 * 1024 / smem : 8;   // resident CTAs per SM
+  int per_sm = 0;   // resident CTAs per SM: the persistent grid is exactly one resident wave
+  KCG_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, TR_THREADS, smem));
+  if (per_sm < 1) per_sm = 1;
   const long long cap = static_cast<long long>(device_sm_count()) * per_sm;
   const int grid = static_cast<int>(total < cap ? total : cap);
   kern<<<grid, TR_THREADS, smem, stream>>>(static_cast<const T*>(x), static_cast<T*>(y), rows, cols,

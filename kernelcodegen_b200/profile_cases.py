@@ -72,7 +72,18 @@ def fmha_fp32(iters):
     return ms, 4.0 * 4 * 16 * 1024 * 1024 * 64
 
 
-CASES = {"gemm_bf16": gemm_bf16, "gemm_3xtf32": gemm_3xtf32, "gemm_3xtf32_large": gemm_3xtf32_large,
+def transpose_fp32(iters):
+    """8192 x 8192 fp32: 256 MiB in, 256 MiB out.  The second figure printed is bytes moved, so the
+    rate reads as GB/s x 1000 in the TFLOP/s column's place (see main)."""
+    dev = torch.device("cuda:0")
+    x = torch.randn((8192, 8192), device=dev)
+    ms = _time(lambda: ops.transpose(x), iters)
+    return ms, 2.0 * x.numel() * 4
+
+
+BYTE_CASES = {"transpose_fp32"}   # the work figure of these cases is bytes, not flop
+
+CASES = {"transpose_fp32": transpose_fp32, "gemm_bf16": gemm_bf16, "gemm_3xtf32": gemm_3xtf32, "gemm_3xtf32_large": gemm_3xtf32_large,
          "fmha_causal": fmha_causal, "fmha_fp32": fmha_fp32}
 
 
@@ -82,7 +93,8 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     ms, flop = CASES[args.case](args.iters)
-    print(f"{args.case}: {ms:.4f} ms/launch  {flop / ms / 1e9:.1f} TFLOP/s  device_status={ops.last_device_status()}")
+    rate = f"{flop / ms / 1e6:.0f} GB/s" if args.case in BYTE_CASES else f"{flop / ms / 1e9:.1f} TFLOP/s"
+    print(f"{args.case}: {ms:.4f} ms/launch  {rate}  device_status={ops.last_device_status()}")
 
 
 if __name__ == "__main__":
