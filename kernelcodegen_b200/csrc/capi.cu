@@ -235,7 +235,11 @@ int kcg_last_device_status(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
   int v = 0;
   if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (v != 0) cudaMemset(p, 0, sizeof(int));
+  if (v != 0) {
+    cudaMemset(p, 0, sizeof(int));
+    // a kernel that gave up may have left arrival counters of the shared-K tail half counted
+    gemm_reset_shared_k_counters();
+  }
   return v;
 }
 

@@ -999,6 +999,13 @@ static void resolve_variant(const kcg_gemm_desc* d, int* bn, bool* pair_mode) {
   *pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM && small_job);
 }
 
+// Zeroes the arrival counters on the current device (after a launch that ended on a bounded wait;
+// the device is idle when this is called).
+void gemm_reset_shared_k_counters() {
+  int* counters = nullptr;
+  if (sk_counters_ptr(&counters) == KCG_OK) cudaMemset(counters, 0, sizeof(int) * SK_ROWS * SK_ROW_INTS);
+}
+
 // Tail tiles the shared-K plan covers for this descriptor on 74 CTA pairs (0 = no shared-K tail).
 int gemm_shared_k_tiles_impl(const kcg_gemm_desc* d) {
   if (!d || d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
