@@ -455,23 +455,44 @@ struct CastArgs {
   uint2* dst[3];
   long long n4[3];
 };
-__global__ void f32_to_bf16_kernel(CastArgs a) {
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(CastArgs a) {
   griddep_launch_dependents();   // the attention kernel may move in as SMs become free
-  const long long total = a.n4[0] + a.n4[1] + a.n4[2];
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    int t = 0;
-    long long k = i;
-    if (k >= a.n4[0]) {
-      k -= a.n4[0];
-      t = 1;
-      if (k >= a.n4[1]) {
-        k -= a.n4[1];
-        t = 2;
-      }
+  const long long n01 = a.n4[0] + a.n4[1], total = n01 + a.n4[2];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // element i of the concatenation Q | K | V -> its source and destination (selects, so that
+  // the argument arrays are never indexed by a run-time value)
+  auto locate = [&](long long i, const float4*& src, uint2*& dst) {
+    if (i < a.n4[0]) {
+      src = a.src[0] + i;
+      dst = a.dst[0] + i;
+    } else if (i < n01) {
+      src = a.src[1] + (i - a.n4[0]);
+      dst = a.dst[1] + (i - a.n4[0]);
+    } else {
+      src = a.src[2] + (i - n01);
+      dst = a.dst[2] + (i - n01);
     }
-    const float4 v = a.src[t][k];
-    a.dst[t][k] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+  };
+  auto convert = [](const float4 v) { return make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w)); };
+  // four independent 16-byte loads in flight per thread before the first store
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    float4 v[4];
+    uint2* dst[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float4* src;
+      locate(i + u * stride, src, dst[u]);
+      v[u] = __ldg(src);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) *dst[u] = convert(v[u]);
+  }
+  for (; i < total; i += stride) {
+    const float4* src;
+    uint2* dst;
+    locate(i, src, dst);
+    *dst = convert(__ldg(src));
   }
 }
 

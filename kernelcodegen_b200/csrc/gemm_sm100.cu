@@ -773,24 +773,38 @@ struct SplitArgs {
   int cols4;
   long long ld;
 };
-__global__ void split_lo_kernel(SplitArgs a, SplitArgs b) {
+__device__ __forceinline__ float4 tf32_residual(const float4 v) {
+  float4 l;
+  l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+  l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+  l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+  l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+  return l;
+}
+__global__ void __launch_bounds__(256) split_lo_kernel(SplitArgs a, SplitArgs b) {
   griddep_launch_dependents();   // the GEMM may move in and set itself up while this runs
-  const long long na = a.rows * a.cols4, nb = b.rows * b.cols4;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < na + nb;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+  const long long na = a.rows * a.cols4, nb = b.rows * b.cols4, n = na + nb;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  auto src_of = [&](long long i) -> const float4* {
     const bool second = i >= na;
     const SplitArgs& s = second ? b : a;
     const long long k = second ? i - na : i;
     const long long r = k / s.cols4;
-    const int c = static_cast<int>(k - r * s.cols4);
-    const float4 v = *reinterpret_cast<const float4*>(s.src + r * s.ld + 4ll * c);
-    float4 l;
-    l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-    l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-    l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-    l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-    reinterpret_cast<float4*>(s.lo)[k] = l;
+    return reinterpret_cast<const float4*>(s.src + r * s.ld + 4ll * (k - r * s.cols4));
+  };
+  auto dst_of = [&](long long i) -> float4* {
+    return i >= na ? reinterpret_cast<float4*>(b.lo) + (i - na) : reinterpret_cast<float4*>(a.lo) + i;
+  };
+  // four independent 16-byte loads in flight per thread before the first store
+  long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < n; i += 4 * stride) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldg(src_of(i + u * stride));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) *dst_of(i + u * stride) = tf32_residual(v[u]);
   }
+  for (; i < n; i += stride) *dst_of(i) = tf32_residual(__ldg(src_of(i)));
 }
 
 inline size_t pad256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
