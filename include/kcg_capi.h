@@ -101,7 +101,7 @@ typedef struct kcg_fmha_desc {
   int32_t B, H;
   int32_t Sq, Skv;
   int32_t D;          /* head dim: 64 or 128 */
-  int32_t dtype_in;   /* kcg_dtype_t of Q, K, V (F32 inputs are rounded to bf16 in scratch) */
+  int32_t dtype_in;   /* kcg_dtype_t of Q, K, V (F32: TF32 products for D = 64, rounded to bf16 for D = 128) */
   int32_t dtype_out;  /* kcg_dtype_t of O */
   int32_t causal;     /* 0 / 1 : query i sees keys j <= i + (Skv - Sq) */
   float scale;        /* multiplies the logits before exp */
@@ -116,7 +116,8 @@ typedef struct kcg_fmha_desc {
  * between all CTA pairs, and the partial sums meet in the workspace).  A launch given only (1),
  * or no workspace for bf16/TF32, runs without the shared-K tail: same result up to fp32
  * summation order, a little slower when the last wave is poorly filled.
- * FMHA with f32 inputs: bf16 copies of Q, K, V. */
+ * FMHA with f32 inputs and head dimension 128: bf16 copies of Q, K, V (head dimension 64 runs TF32
+ * contractions on the fp32 arrays and needs none). */
 size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d);
 size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d);
 

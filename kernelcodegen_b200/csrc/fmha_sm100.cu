@@ -24,6 +24,12 @@
 // exists.  Registers are re-balanced with setmaxnreg: the softmax warpgroups hold an O row of D
 // floats per thread, the producer/issuer warpgroup needs next to nothing.
 //
+// fp32 inputs with head dimension 64 (TF = true) run both contractions as TF32 products straight
+// from the fp32 tiles: Q and K as K-major 128B-swizzled panels of 32 floats, V as an MN-major
+// operand in the 32-byte-atom swizzle, P written back over S as fp32 (the tensor core truncates
+// fp32 operands to TF32 itself).  No conversion pass, and three more mantissa bits than bf16.
+// Other fp32 shapes are rounded to bf16 by a separate pass into the workspace first.
+//
 // Online softmax: m_j = max(m_{j-1}, rowmax(S_j)), alpha_j = exp(scale*(m_{j-1}-m_j)),
 // l_j = alpha_j*l_{j-1} + rowsum(P_j), O_j = alpha_j*O_{j-1} + P_j.V_j, out = O_n / l_n --
 // mathematically the reference's exp(x)/sum(exp(x)) (no max subtraction there), evaluated
@@ -54,10 +60,14 @@ struct FmhaParams {
   int after_cast;    // the inputs come from the cast launch just before (programmatic dependent launch)
 };
 
-template <int D>
+template <int D, bool TF>
 struct FmhaCfg {
-  static constexpr int TILE_BYTES = 128 * D * 2;      // Q_t, K_j, V_j tile: 128 rows x D bf16
-  static constexpr int PANEL_BYTES = 128 * 128;       // 128 rows x 64 bf16 (one swizzle panel)
+  static constexpr int ES = TF ? 4 : 2;               // bytes per operand element
+  static constexpr int TILE_BYTES = 128 * D * ES;     // Q_t, K_j, V_j tile: 128 rows x D elements
+  static constexpr int PANEL_BYTES = 128 * 128;       // 128 rows x 128 bytes (one swizzle panel)
+  static constexpr int PANEL_ELEMS = 128 / ES;        // 64 bf16 or 32 fp32 per panel row
+  static constexpr int DPANELS = D / PANEL_ELEMS;
+  static constexpr int UMMA_K = 32 / ES;              // elements of K per UMMA: 16 bf16 or 8 fp32
   static constexpr int SMEM_DATA = QTILES * TILE_BYTES + 2 * TILE_BYTES /*K*/ + 2 * TILE_BYTES /*V*/;
   static constexpr int SMEM_TOTAL = SMEM_DATA + 1024 /*ctrl*/ + 1024 /*align slack*/;
   static constexpr int TMEM_COLS = 512;               // S0 | S1 | PV0 | PV1
@@ -75,16 +85,19 @@ __device__ __forceinline__ void reg_alloc_224() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
 }
 
-template <int D>
+template <int D, bool TF>
 __global__ void __launch_bounds__(FM_THREADS, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FmhaParams p) {
-  using Cfg = FmhaCfg<D>;
+  using Cfg = FmhaCfg<D, TF>;
   constexpr int TILE = Cfg::TILE_BYTES;
   constexpr int PANEL = Cfg::PANEL_BYTES;
-  constexpr int DPANELS = D / 64;
-  constexpr uint32_t IDESC_S = make_idesc(UMMA_FMT_BF16, BQ, BKV, 0, 0);
-  constexpr uint32_t IDESC_PV = make_idesc(UMMA_FMT_BF16, BQ, D, 0, 1);
+  constexpr int DPANELS = Cfg::DPANELS;
+  constexpr int PW = Cfg::PANEL_ELEMS;
+  constexpr int UK = Cfg::UMMA_K;
+  constexpr uint32_t FMT = TF ? UMMA_FMT_TF32 : UMMA_FMT_BF16;
+  constexpr uint32_t IDESC_S = make_idesc(FMT, BQ, BKV, 0, 0);
+  constexpr uint32_t IDESC_PV = make_idesc(FMT, BQ, D, 0, 1);
   constexpr uint32_t TM_S = 0, TM_O = 256;            // + 128 * tile
 
   extern __shared__ uint8_t smem_raw[];
@@ -166,7 +179,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_expect_tx(bar_q + 8 * t, TILE);
 #pragma unroll
         for (int dp = 0; dp < DPANELS; ++dp)
-          tma_load_3d(sQ + t * TILE + dp * PANEL, &tmQ, bar_q + 8 * t, dp * 64, q0 + t * BQ, bh);
+          tma_load_3d(sQ + t * TILE + dp * PANEL, &tmQ, bar_q + 8 * t, dp * PW, q0 + t * BQ, bh);
       }
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
@@ -177,13 +190,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_expect_tx(bar_kfull + 8 * b, TILE);
 #pragma unroll
         for (int dp = 0; dp < DPANELS; ++dp)
-          tma_load_3d(sK + b * TILE + dp * PANEL, &tmK, bar_kfull + 8 * b, dp * 64, j * BKV, bh);
+          tma_load_3d(sK + b * TILE + dp * PANEL, &tmK, bar_kfull + 8 * b, dp * PW, j * BKV, bh);
         ok = mbar_wait(bar_vempty + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_PRODUCER, p.spin);
         if (!ok) break;
         mbar_expect_tx(bar_vfull + 8 * b, TILE);
 #pragma unroll
         for (int dp = 0; dp < DPANELS; ++dp)
-          tma_load_3d(sV + b * TILE + dp * PANEL, &tmV, bar_vfull + 8 * b, dp * 64, j * BKV, bh);
+          tma_load_3d(sV + b * TILE + dp * PANEL, &tmV, bar_vfull + 8 * b, dp * PW, j * BKV, bh);
       }
       if (!ok) {
         // give copies already in flight time to land before shared memory is released
@@ -206,7 +219,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // bits of the descriptor, never overflowing: shared memory is < 256 KB) is advanced.
       const uint64_t q_desc0 = make_smem_desc(sQ, 16, 1024);
       const uint64_t k_desc0 = make_smem_desc(sK, 16, 1024);
-      const uint64_t v_desc0 = make_smem_desc(sV, PANEL, 1024);
+      // V is the MN-major operand (head dimension contiguous): fp32 tiles use the 32-byte-atom
+      // form of the 128B swizzle (4-row period, stride-byte-offset 512)
+      const uint64_t v_desc0 = TF ? make_smem_desc(sV, PANEL, 512, SMEM_LAYOUT_SW128_ATOM32)
+                                  : make_smem_desc(sV, PANEL, 1024);
       constexpr uint64_t TILE16 = TILE >> 4;
       auto issue_s = [&](int t, int j) {
         // S_t(j) = Q_t . K_j^T; the caller has waited for K_j and for the S_t buffer
@@ -214,26 +230,34 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t d_tmem = tmem_base + TM_S + t * BKV;
         if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
+          for (int ks = 0; ks < D / UK; ++ks) {   // 32 bytes of K per instruction, 4 per panel
             const uint64_t off = static_cast<uint64_t>(((ks >> 2) * PANEL + (ks & 3) * 32) >> 4);
-            umma_bf16_ss(d_tmem, qd + off, kd + off, IDESC_S, ks ? 1u : 0u);
+            if (TF)
+              umma_tf32_ss(d_tmem, qd + off, kd + off, IDESC_S, ks ? 1u : 0u);
+            else
+              umma_bf16_ss(d_tmem, qd + off, kd + off, IDESC_S, ks ? 1u : 0u);
           }
           umma_commit(bar_sfull + 8 * t);
         }
         __syncwarp();
       };
       auto issue_pv = [&](int t, int j) {
-        // O_t (+)= P_t(j) . V_j with P_t in the TMEM columns of S_t (16 keys = 8 columns); the
-        // accumulator stays in TMEM across blocks, the softmax warps rescale it in place when the
-        // row maximum moves.  V tile: D/64 groups of [128 keys x 128 bytes]; 16 keys = 2048 bytes.
+        // O_t (+)= P_t(j) . V_j with P_t in the TMEM columns of S_t (one instruction takes 8
+        // columns: 16 bf16 keys, two per column, or 8 fp32 keys); the accumulator stays in TMEM
+        // across blocks, the softmax warps rescale it in place when the row maximum moves.
+        // V tile: groups of [128 keys x 128 bytes]; one instruction's keys are UK * 128 bytes.
         const uint64_t vd = v_desc0 + (j & 1) * TILE16;
         const uint32_t d_tmem = tmem_base + TM_O + t * 128;
         const uint32_t a_tmem = tmem_base + TM_S + t * BKV;
         if (elect_one()) {
-          umma_bf16_ts(d_tmem, a_tmem, vd, IDESC_PV, j ? 1u : 0u);
 #pragma unroll
-          for (int ks = 1; ks < BKV / 16; ++ks)
-            umma_bf16_ts(d_tmem, a_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), IDESC_PV, 1u);
+          for (int ks = 0; ks < BKV / UK; ++ks) {
+            const uint64_t vk = vd + static_cast<uint64_t>((ks * UK * 128) >> 4);
+            if (TF)
+              umma_tf32_ts(d_tmem, a_tmem + ks * 8, vk, IDESC_PV, (j | ks) ? 1u : 0u);
+            else
+              umma_bf16_ts(d_tmem, a_tmem + ks * 8, vk, IDESC_PV, (j | ks) ? 1u : 0u);
+          }
           umma_commit(bar_pvfull + 8 * t);
         }
         __syncwarp();
@@ -373,25 +397,43 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float2 rsg[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) rsg[g] = make_float2(0.f, 0.f);
+      if (TF) {
+        // P stays fp32 (the tensor core reads it as TF32), over all 128 columns of this S buffer
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int g = 0; g < 2; ++g)
+        for (int g = 0; g < 4; ++g) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float2 x = fma2(make_float2(__uint_as_float(sr[2 * hh + g][i]), __uint_as_float(sr[2 * hh + g][i + 1])),
-                            make_float2(c, c), make_float2(-mc, -mc));
-            if (((i >> 1) & 7) < POLY_PER_8) {
-              x = exp2_poly2(x);
-            } else {
-              x.x = ex2_approx(x.x);
-              x.y = ex2_approx(x.y);
-            }
+            float2 x = fma2(make_float2(__uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1])), make_float2(c, c),
+                            make_float2(-mc, -mc));
+            x.x = ex2_approx(x.x);
+            x.y = ex2_approx(x.y);
             rsg[(i >> 1) & 3] = add2(rsg[(i >> 1) & 3], x);
-            pk[16 * g + (i >> 1)] = pack_bf16x2(x.x, x.y);
+            sr[g][i] = __float_as_uint(x.x);
+            sr[g][i + 1] = __float_as_uint(x.y);
           }
-        tmem_st_32x32(t_s + 32 * hh, pk);
+          tmem_st_32x32(t_s + 32 * g, sr[g]);
+        }
+      } else {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float2 x = fma2(make_float2(__uint_as_float(sr[2 * hh + g][i]), __uint_as_float(sr[2 * hh + g][i + 1])),
+                              make_float2(c, c), make_float2(-mc, -mc));
+              if (((i >> 1) & 7) < POLY_PER_8) {
+                x = exp2_poly2(x);
+              } else {
+                x.x = ex2_approx(x.x);
+                x.y = ex2_approx(x.y);
+              }
+              rsg[(i >> 1) & 3] = add2(rsg[(i >> 1) & 3], x);
+              pk[16 * g + (i >> 1)] = pack_bf16x2(x.x, x.y);
+            }
+          tmem_st_32x32(t_s + 32 * hh, pk);
+        }
       }
       const float2 rs2 = add2(add2(rsg[0], rsg[1]), add2(rsg[2], rsg[3]));
       tmem_st_wait();
@@ -498,12 +540,12 @@ __global__ void __launch_bounds__(256) f32_to_bf16_kernel(CastArgs a) {
 
 inline size_t pad256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
-template <int D>
+template <int D, bool TF = false>
 kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          const FmhaParams& p, int bh, cudaStream_t stream, bool after_cast) {
-  using Cfg = FmhaCfg<D>;
+  using Cfg = FmhaCfg<D, TF>;
   static_assert(Cfg::SMEM_TOTAL <= 232448, "shared memory budget");
-  auto kern = fmha_fwd_kernel<D>;
+  auto kern = fmha_fwd_kernel<D, TF>;
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::SMEM_TOTAL));
   dim3 grid((p.Sq + QTILES * BQ - 1) / (QTILES * BQ), bh);
@@ -528,6 +570,7 @@ kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 
 size_t fmha_workspace_impl(const kcg_fmha_desc* d) {
   if (!d || d->dtype_in != KCG_F32) return 0;
+  if (d->D == 64) return 0;   // TF32 contractions straight from the fp32 tiles
   if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0 || d->D <= 0) return 0;
   const size_t bh = static_cast<size_t>(d->B) * d->H;
   return pad256(bh * d->Sq * d->D * 2) + 2 * pad256(bh * d->Skv * d->D * 2);
@@ -549,7 +592,8 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
   const void* q = Q;
   const void* k = K;
   const void* v = V;
-  if (d->dtype_in == KCG_F32) {
+  const bool tf = d->dtype_in == KCG_F32 && d->D == 64;   // TF32 contractions on the fp32 tiles
+  if (d->dtype_in == KCG_F32 && !tf) {
     const size_t need = fmha_workspace_impl(d);
     if (!ws || ws_bytes < need || !aligned16(ws)) return KCG_BAD_WORKSPACE;
     uint8_t* w = static_cast<uint8_t*>(ws);
@@ -574,23 +618,28 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
     v = vb;
   }
   CUtensorMap tq, tk, tv;
-  const uint32_t box[3] = {64, 128, 1};
+  // one 128-byte swizzle panel of a tile per copy: 64 bf16 or 32 fp32 wide, 128 rows
+  const uint32_t box[3] = {tf ? 32u : 64u, 128, 1};
+  const CUtensorMapDataType dt = tf ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint64_t es = tf ? 4 : 2;
+  // fp32 V is an MN-major operand: 32-byte-atom form of the 128B swizzle
+  const CUtensorMapSwizzle sw_v = tf ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(d->D), static_cast<uint64_t>(d->Sq),
                               static_cast<uint64_t>(bh)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(d->D) * 2,
-                                 static_cast<uint64_t>(d->Sq) * d->D * 2};
-    kcg_status_t st = encode_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, q, dims, strides, box);
+    const uint64_t strides[2] = {static_cast<uint64_t>(d->D) * es,
+                                 static_cast<uint64_t>(d->Sq) * d->D * es};
+    kcg_status_t st = encode_tmap(&tq, dt, 3, q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != KCG_OK) return st;
   }
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(d->D), static_cast<uint64_t>(d->Skv),
                               static_cast<uint64_t>(bh)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(d->D) * 2,
-                                 static_cast<uint64_t>(d->Skv) * d->D * 2};
-    kcg_status_t st = encode_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, k, dims, strides, box);
+    const uint64_t strides[2] = {static_cast<uint64_t>(d->D) * es,
+                                 static_cast<uint64_t>(d->Skv) * d->D * es};
+    kcg_status_t st = encode_tmap(&tk, dt, 3, k, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != KCG_OK) return st;
-    st = encode_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, v, dims, strides, box);
+    st = encode_tmap(&tv, dt, 3, v, dims, strides, box, sw_v);
     if (st != KCG_OK) return st;
   }
   FmhaParams p;
@@ -604,7 +653,8 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
   if (st != KCG_OK) return st;
   const uint32_t spin = g_spin_limit.load();
   p.spin = spin ? spin : KCG_SPIN_LIMIT;
-  if (d->D == 64) return launch_fmha<64>(tq, tk, tv, p, bh, stream, d->dtype_in == KCG_F32);
+  if (tf) return launch_fmha<64, true>(tq, tk, tv, p, bh, stream, false);
+  if (d->D == 64) return launch_fmha<64>(tq, tk, tv, p, bh, stream, false);
   return launch_fmha<128>(tq, tk, tv, p, bh, stream, d->dtype_in == KCG_F32);
 }
 

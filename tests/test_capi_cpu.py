@@ -67,9 +67,12 @@ def test_workspace_sizes(native_lib):
     d = _gemm_desc(4096, 4096, 4096, prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)      # 256 tiles of 256x256
     assert native_lib.kcg_gemm_shared_k_tiles(ctypes.byref(d)) == 34
     f = capi.FmhaDesc()
-    f.B, f.H, f.Sq, f.Skv, f.D = 2, 3, 128, 256, 64
-    f.dtype_in = capi.KCG_F32
-    assert native_lib.kcg_fmha_workspace_bytes(ctypes.byref(f)) == 2 * 3 * 64 * 2 * (128 + 2 * 256)
+    f.B, f.H, f.Sq, f.Skv, f.D = 2, 3, 128, 256, 128
+    f.dtype_in = capi.KCG_F32          # head dimension 128: bf16 copies of Q, K, V in the workspace
+    assert native_lib.kcg_fmha_workspace_bytes(ctypes.byref(f)) == 2 * 3 * 128 * 2 * (128 + 2 * 256)
+    f.D = 64                           # head dimension 64: TF32 contractions on the fp32 tiles, no scratch
+    assert native_lib.kcg_fmha_workspace_bytes(ctypes.byref(f)) == 0
+    f.D = 128
     f.dtype_in = capi.KCG_BF16
     assert native_lib.kcg_fmha_workspace_bytes(ctypes.byref(f)) == 0
 
@@ -120,7 +123,8 @@ def test_fmha_argument_validation_needs_no_gpu(native_lib):
     f.scale = 1.0
     f.dtype_in = 3
     assert call() == capi.KCG_UNSUPPORTED
-    f.dtype_in = capi.KCG_F32  # f32 inputs need scratch for their bf16 copies
+    f.dtype_in = capi.KCG_F32  # f32 inputs with head dimension 128 need scratch for their bf16 copies
+    f.D = 128
     assert call() == capi.KCG_BAD_WORKSPACE
     assert native_lib.kcg_fmha_fwd_launch(None, fake, fake, fake, fake, None, 0, None) == capi.KCG_BAD_ARGUMENT
 

@@ -15,6 +15,7 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 BF16_TOL = 2e-2
+TF32_TOL = 5e-3   # fp32 inputs, head dimension 64: both contractions as TF32 products
 
 
 def rel_err(x, ref):
@@ -56,6 +57,33 @@ def test_small_shapes_vs_oracle(cuda_device, b, h, sq, skv, d, causal):
     assert ops.last_device_status() == 0
 
 
+@pytest.mark.parametrize("b,h,sq,skv,d", [(1, 1, 128, 128, 64), (2, 3, 200, 200, 64), (1, 1, 1, 17, 64), (1, 2, 520, 392, 64),
+                                          (3, 1, 256, 1030, 64), (1, 2, 200, 328, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp32_inputs_small_shapes_vs_oracle(cuda_device, b, h, sq, skv, d, causal):
+    """fp32 Q, K, V.  Head dimension 64: TF32 contractions straight from the fp32 tiles, held to
+    the TF32 bar against the oracle on the un-rounded inputs.  Head dimension 128: rounded to bf16
+    by a separate pass, the same bits as the bf16-input kernel gets from pre-rounded inputs."""
+    from kernelcodegen_b200 import ops
+
+    q, k, v = normal((b, h, sq, d), 11), normal((b, h, skv, d), 12), normal((b, h, skv, d), 13)
+    scale = 1.0 / math.sqrt(d)
+    got = ops.fmha(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), scale=scale, causal=causal)
+    assert got.dtype == torch.float32 and torch.isfinite(got).all()
+    if d == 64:
+        want = oracle.fmha(q.numpy(), k.numpy(), v.numpy(), scale=scale, causal=causal, threads=0)
+        err = rel_err(got.cpu().numpy(), want)
+        assert err <= TF32_TOL, err
+    else:
+        want = oracle.fmha(q.bfloat16().float().numpy(), k.bfloat16().float().numpy(), v.bfloat16().float().numpy(),
+                           scale=scale, causal=causal, threads=0)
+        assert rel_err(got.cpu().numpy(), want) <= BF16_TOL
+        pre = ops.fmha(q.bfloat16().to(cuda_device), k.bfloat16().to(cuda_device), v.bfloat16().to(cuda_device),
+                       scale=scale, causal=causal, out_dtype=torch.float32)
+        assert torch.equal(got, pre)
+    assert ops.last_device_status() == 0
+
+
 def test_reference_graph_no_scale_no_mask(cuda_device):
     """scale = 1, causal = off: exactly BatchedMatmul -> Softmax -> BatchedMatmul of the reference."""
     from kernelcodegen_b200 import ops
@@ -77,12 +105,11 @@ def test_config_fp32_b4_h16_s1024_d64(cuda_device):
     got = ops.fmha(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), scale=0.125)
     assert got.dtype == torch.float32
     pick = [0, 9, 18, 27, 36, 45, 54, 63]
-    qb, kb, vb = (t.bfloat16().float().reshape(64, 1024, 64)[pick].numpy() for t in (q, k, v))
-    want = oracle.fmha(qb, kb, vb, scale=0.125, threads=0)
-    assert rel_err(got.reshape(64, 1024, 64)[pick].cpu().numpy(), want) <= BF16_TOL
-    # against the un-rounded fp32 inputs the error is still inside the bf16 bar
-    want32 = oracle.fmha(*(t.reshape(64, 1024, 64)[pick[:2]].numpy() for t in (q, k, v)), scale=0.125, threads=0)
-    assert rel_err(got.reshape(64, 1024, 64)[pick[:2]].cpu().numpy(), want32) <= BF16_TOL
+    # head dimension 64 with fp32 inputs runs both contractions as TF32 products of the fp32
+    # tiles: compared with the oracle on the un-rounded inputs, at the TF32 bar
+    want32 = oracle.fmha(*(t.reshape(64, 1024, 64)[pick].numpy() for t in (q, k, v)), scale=0.125, threads=0)
+    err = rel_err(got.reshape(64, 1024, 64)[pick].cpu().numpy(), want32)
+    assert err <= TF32_TOL, err
     assert ops.last_device_status() == 0
 
 
