@@ -161,7 +161,7 @@ def test_generated_launcher_text_compiles(stages, tmp_path):
 def test_reference_driver_compiles_unchanged(tmp_path):
     """The reference's own test program (it names only the public API and uses `auto` for IR
     handles) builds against these headers.  Only where the reference tree is mounted."""
-    ref = Path("/root/reference/test/test.cc")
+    ref = ROOT.parent / "reference" / "test" / "test.cc"   # the reference tree, where it sits beside this repository
     if not ref.exists():
         pytest.skip("reference tree not present")
     from kernelcodegen_b200 import build
