@@ -38,7 +38,8 @@ __global__ void __launch_bounds__(TR_THREADS) transpose_kernel(const T* __restri
   T(*tile)[TT + PAD] = reinterpret_cast<T(*)[TT + PAD]>(tr_smem);
   const int tr = threadIdx.x >> 4;          // 0..15: row within a 16-row pass
   const int tc = (threadIdx.x & 15) * VW;   // first of this thread's VW columns
-  for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+  // where tile t lies, and whether it takes the vector path
+  auto locate = [&](long long t, const T*& xb, T*& yb, long long& i0, long long& j0) -> bool {
     const long long b = t / tiles_per_mat;
     const long long r = t - b * tiles_per_mat;
     // Tiles are walked in bands of 8 tile rows, column by column inside a band, so the CTAs that
@@ -47,20 +48,53 @@ __global__ void __launch_bounds__(TR_THREADS) transpose_kernel(const T* __restri
     const long long band = r / (8ll * tiles_c);
     const long long in_band = r - band * 8ll * tiles_c;
     const long long band_rows = min(8ll, tiles_r - band * 8);
-    const long long i0 = (band * 8 + in_band % band_rows) * TT, j0 = (in_band / band_rows) * TT;
-    const T* xb = x + b * rows * cols;
-    T* yb = y + b * rows * cols;
-    const bool full = vec_ok && i0 + TT <= rows && j0 + TT <= cols;
+    i0 = (band * 8 + in_band % band_rows) * TT;
+    j0 = (in_band / band_rows) * TT;
+    xb = x + b * rows * cols;
+    yb = y + b * rows * cols;
+    return vec_ok && i0 + TT <= rows && j0 + TT <= cols;
+  };
+  auto fetch = [&](const T* xb, long long i0, long long j0, uint4 (&v)[PASSES]) {
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p)
+      v[p] = __ldg(reinterpret_cast<const uint4*>(xb + (i0 + tr + 16 * p) * cols + j0 + tc));
+  };
+  // The loads of a CTA's next tile are issued before the stores of the current one, so reads
+  // and writes of one CTA overlap instead of alternating.
+  uint4 nxt[PASSES];
+  {
+    const T* xb;
+    T* yb;
+    long long i0, j0;
+    if (blockIdx.x < total_tiles && locate(blockIdx.x, xb, yb, i0, j0)) fetch(xb, i0, j0, nxt);
+  }
+  for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const T* xb;
+    T* yb;
+    long long i0, j0;
+    const bool full = locate(t, xb, yb, i0, j0);
     if (full) {
 #pragma unroll
       for (int p = 0; p < PASSES; ++p) {
-        const int i = tr + 16 * p;
         Pack16<T> v;
-        v.v = *reinterpret_cast<const uint4*>(xb + (i0 + i) * cols + j0 + tc);
+        v.v = nxt[p];
 #pragma unroll
-        for (int k = 0; k < VW; ++k) tile[i][tc + k] = v.e[k];
+        for (int k = 0; k < VW; ++k) tile[tr + 16 * p][tc + k] = v.e[k];
       }
-      __syncthreads();
+    } else {
+      for (int idx = threadIdx.x; idx < TT * TT; idx += TR_THREADS) {
+        const int i = idx / TT, j = idx % TT;
+        if (i0 + i < rows && j0 + j < cols) tile[i][j] = xb[(i0 + i) * cols + j0 + j];
+      }
+    }
+    __syncthreads();
+    {
+      const T* xn;
+      T* yn;
+      long long in0, jn0;
+      if (t + gridDim.x < total_tiles && locate(t + gridDim.x, xn, yn, in0, jn0)) fetch(xn, in0, jn0, nxt);
+    }
+    if (full) {
 #pragma unroll
       for (int p = 0; p < PASSES; ++p) {
         const int j = tr + 16 * p;          // row of Y inside the tile = column of X
@@ -70,11 +104,6 @@ __global__ void __launch_bounds__(TR_THREADS) transpose_kernel(const T* __restri
         *reinterpret_cast<uint4*>(yb + (j0 + j) * rows + i0 + tc) = v.v;
       }
     } else {
-      for (int idx = threadIdx.x; idx < TT * TT; idx += TR_THREADS) {
-        const int i = idx / TT, j = idx % TT;
-        if (i0 + i < rows && j0 + j < cols) tile[i][j] = xb[(i0 + i) * cols + j0 + j];
-      }
-      __syncthreads();
       for (int idx = threadIdx.x; idx < TT * TT; idx += TR_THREADS) {
         const int j = idx / TT, i = idx % TT;
         if (i0 + i < rows && j0 + j < cols) yb[(j0 + j) * rows + i0 + i] = tile[i][j];
