@@ -503,40 +503,54 @@ def run_ours(args):
                 "per_gpu": True, "flop_per_launch": 2.0 * rows * N * K, "kernel_ms": kernel_ms}
 
     # end to end through the public API with host buffers: H2D of this rank's A block and of B,
-    # launch, D2H of this rank's C block, every step
+    # launch, D2H of this rank's C block, every step.  With several ranks each one copies only its
+    # 1/N row block of B over its own PCIe link and the blocks are all-gathered over NVLink.
     a_host = torch.empty((rows, K), dtype=torch.bfloat16).pin_memory()
     a_host.copy_(a)
-    b_host = torch.empty((K, N), dtype=torch.bfloat16).pin_memory()
-    b_host.copy_(b)
+    share_b = dist is not None and K % world == 0
+    klo, khi = sharding.row_block(K, rank, world) if share_b else (0, K)
+    b_host = torch.empty((khi - klo, N), dtype=torch.bfloat16).pin_memory()   # this rank's row block of B (all of B at N = 1)
+    b_host.copy_(b[klo:khi])
+    b_blk = torch.empty((khi - klo, N), dtype=torch.bfloat16, device=dev) if share_b else None
     c_host = torch.empty((rows, N), dtype=torch.bfloat16).pin_memory()
 
     def e2e_step():
-        # kcg_gemm_host_staged: chunked H2D of A and B, GEMM strips as chunks land, D2H of finished
-        # strips of C, on the library's three streams; the current stream continues after the last D2H
-        ops.matmul_host(a_host, b_host, c_host, a, b, c_local, relu=True, peers=peers, chunks=args.e2e_chunks)
+        # kcg_gemm_host_staged: chunked H2D, GEMM strips as chunks land, D2H of finished strips of C,
+        # on the library's three streams; the current stream continues after the last D2H
+        if not share_b:
+            ops.matmul_host(a_host, b_host, c_host, a, b, c_local, relu=True, peers=peers, chunks=args.e2e_chunks)
+        else:
+            b_blk.copy_(b_host, non_blocking=True)
+            dist.all_gather_into_tensor(b, b_blk)          # row blocks of B, rank order = row order
+            ops.matmul_host(a_host, None, c_host, a, b, c_local, relu=True, peers=peers, chunks=args.e2e_chunks)
         if dist is not None:
             dist.all_reduce(sync_token)
 
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = time_steps(e2e_step, e2e_steps, 1, torch, dist) / e2e_steps
     e2e = {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "h2d_bytes_per_step": (rows * K + K * N) * 2 * world, "d2h_bytes_per_step": rows * N * 2 * world,
-           "note": "pinned host A row block + B -> device, GEMM, C row block -> host, per rank, every step, through "
-                   "kcg_gemm_host_staged (row chunks of A / column chunks of B copied alternately, each GEMM strip launched "
-                   "when its operands have landed, finished strips of C copied back meanwhile)"}
+           "h2d_bytes_per_step": (M * K + K * N) * 2, "d2h_bytes_per_step": M * N * 2,
+           "note": ("pinned host A + B -> device, GEMM, C -> host, every step, through kcg_gemm_host_staged (row chunks of A / "
+                    "column chunks of B copied alternately, each GEMM strip launched when its operands have landed, finished "
+                    "strips of C copied back meanwhile)") if not share_b else
+                   ("per rank, every step: pinned host A row block and 1/N of B -> device, B all-gathered over NVLink (NCCL), "
+                    "kcg_gemm_host_staged on the resident B (row chunks of A in, GEMM strips, strips of C out)")}
     # the strips that came back are the product the device holds
     e2e["c_host_equals_device"] = bool(torch.equal(c_host[:256], c_local[:256].cpu()) and
                                        torch.equal(c_host[-256:], c_local[-256:].cpu()))
 
-    def e2e_sequential():  # for comparison only: the same copies and launch one after the other
+    def e2e_sequential():  # for comparison only: every rank copies all it needs, then launches, then copies back
         a.copy_(a_host, non_blocking=True)
-        b.copy_(b_host, non_blocking=True)
+        b.copy_(b_full_host, non_blocking=True)
         ops.matmul_relu(a, b, out=c_local, peers=peers)
         if dist is not None:
             dist.all_reduce(sync_token)
         c_host.copy_(c_local, non_blocking=True)
+    b_full_host = b_host if not share_b else torch.empty((K, N), dtype=torch.bfloat16).pin_memory()
+    if share_b:
+        b_full_host.copy_(b)
     e2e["ms_per_step_sequential"] = time_steps(e2e_sequential, 2, 1, torch, dist) / 2
-    del a_host, b_host, c_host
+    del a_host, b_host, b_full_host, b_blk, c_host
 
     others = []
     tf32_peak = None

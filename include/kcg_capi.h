@@ -197,6 +197,9 @@ kcg_status_t kcg_gemm_host(const kcg_gemm_desc* d, const void* hA, const void* h
  * device; they start after the work already queued on `stream`, and `stream` continues once the
  * last strip of C is on the host, so the caller only synchronises `stream`.  d->peer_c, when set,
  * receives every strip as in kcg_gemm_launch.  `workspace` as for kcg_gemm_launch with `d`.
+ * hB may be NULL: B is then taken as already present in dB (a multi-GPU caller that copies 1/N of
+ * B over its own PCIe link and gathers the rest from its peers over NVLink before this call);
+ * only the row chunks of A and the strips of C move.
  * The device-side status is not read here: call kcg_last_device_status after synchronising. */
 kcg_status_t kcg_gemm_host_staged(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC, void* dA,
                                   void* dB, void* dC, void* workspace, size_t workspace_bytes, int chunks,

@@ -9,7 +9,9 @@
 // landed the kernel runs on it against row chunks 0..k.  Every C tile is computed once, as early
 // as its operands allow, and only 1/chunks of the work is left when the last copy ends.  Finished
 // strips of C go back to the host on a third stream, in the other PCIe direction.  Three streams,
-// ordered by events only; nothing blocks the host.
+// ordered by events only; nothing blocks the host.  With B already on the device (hB == nullptr: a
+// caller that fetched B some other way, e.g. 1/N of it over PCIe and the rest from its peers over
+// NVLink) only the row chunks of A and the strips of C move.
 #include <algorithm>
 #include <mutex>
 
@@ -70,7 +72,8 @@ inline cudaError_t copy_block(void* dst, const void* src, long long ld, long lon
 kcg_status_t gemm_host_staged_impl(const kcg_gemm_desc* d, const void* hA, const void* hB, void* hC, void* dA,
                                    void* dB, void* dC, void* ws, size_t ws_bytes, int chunks,
                                    cudaStream_t stream) {
-  if (!d || !hA || !hB || !hC || !dA || !dB || !dC) return KCG_BAD_ARGUMENT;
+  if (!d || !hA || !hC || !dA || !dB || !dC) return KCG_BAD_ARGUMENT;
+  const bool b_resident = hB == nullptr;   // B is already in dB (put there by the caller, e.g. gathered from peers)
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
   if (chunks < 0 || chunks > MAX_CHUNKS) return KCG_BAD_ARGUMENT;
   if (d->n_peers < 0 || d->n_peers > 8) return KCG_BAD_ARGUMENT;
@@ -85,7 +88,7 @@ kcg_status_t gemm_host_staged_impl(const kcg_gemm_desc* d, const void* hA, const
   // chunks of about 2048 rows / columns, at most 16 per dimension; one chunk (no overlap) for
   // products too small to hide a copy behind
   const int nr_want = chunks ? chunks : static_cast<int>(std::max<long long>(1, std::min<long long>(MAX_CHUNKS, M / 2048)));
-  const int nc_want = chunks ? chunks : static_cast<int>(std::max<long long>(1, std::min<long long>(MAX_CHUNKS, N / 2048)));
+  const int nc_want = b_resident ? 1 : (chunks ? chunks : static_cast<int>(std::max<long long>(1, std::min<long long>(MAX_CHUNKS, N / 2048))));
   const long long rh = round_up((M + nr_want - 1) / nr_want, 256);  // rows of A per chunk (tile aligned)
   const long long cw = round_up((N + nc_want - 1) / nc_want, 256);  // columns of B per chunk
   const int nr = static_cast<int>((M + rh - 1) / rh), nc = static_cast<int>((N + cw - 1) / cw);
@@ -147,7 +150,8 @@ kcg_status_t gemm_host_staged_impl(const kcg_gemm_desc* d, const void* hA, const
     const long long r_hi = std::min(M, (std::min(k, nr - 1) + 1) * rh);
     const long long b_r0 = bk ? c0 : 0, b_c0 = bk ? 0 : c0;
     const long long b_rows = bk ? c1 - c0 : K, b_cols = bk ? K : c1 - c0;
-    PIPE_TRY(copy_block(dB, hB, d->ldb, b_r0, b_c0, b_rows, b_cols, es, cudaMemcpyHostToDevice, cx->h2d));
+    if (!b_resident)
+      { PIPE_TRY(copy_block(dB, hB, d->ldb, b_r0, b_c0, b_rows, b_cols, es, cudaMemcpyHostToDevice, cx->h2d)); }
     PIPE_TRY(cudaEventRecord(cx->in_done[2 * k + 1], cx->h2d));
     PIPE_TRY(cudaStreamWaitEvent(cx->compute, cx->in_done[2 * k + 1], 0));
     st = strip(0, r_hi, c0, c1);

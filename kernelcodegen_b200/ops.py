@@ -106,16 +106,18 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, relu: bool = False, precision: O
     return out
 
 
-def matmul_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor, a_dev: torch.Tensor,
+def matmul_host(a_host: torch.Tensor, b_host: Optional[torch.Tensor], c_host: torch.Tensor, a_dev: torch.Tensor,
                 b_dev: torch.Tensor, c_dev: torch.Tensor, *, relu: bool = False, precision: Optional[str] = None,
                 b_col_major: bool = False, chunks: int = 0, peers: Sequence[int] = ()) -> torch.Tensor:
     """c_host = A . B from HOST arrays (pin them for the copies to overlap), staged through the
     caller's device arrays of the same shapes: row chunks of A and column chunks of B are copied
     while the kernel already runs on the tiles that have arrived, and finished strips of C return
-    to the host meanwhile (`kcg_gemm_host_staged`).  Asynchronous: synchronise the current stream
-    before reading `c_host`."""
+    to the host meanwhile (`kcg_gemm_host_staged`).  `b_host=None`: B is already in `b_dev`.
+    Asynchronous: synchronise the current stream before reading `c_host`."""
     dev = _require_cuda(a_dev, b_dev, c_dev)
     for h, t in ((a_host, a_dev), (b_host, b_dev), (c_host, c_dev)):
+        if h is None and t is b_dev:
+            continue
         if h.is_cuda or h.shape != t.shape or h.dtype != t.dtype or h.stride() != t.stride():
             raise ValueError("host and device arrays must match in shape, dtype and strides")
         if h.dim() != 2 or h.stride(1) != 1:
@@ -140,7 +142,8 @@ def matmul_host(a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor
     with torch.cuda.device(dev):
         ws_bytes = lib.kcg_gemm_workspace_bytes(ctypes.byref(d))
         ws = _workspace(dev, ws_bytes)
-        st = lib.kcg_gemm_host_staged(ctypes.byref(d), a_host.data_ptr(), b_host.data_ptr(), c_host.data_ptr(),
+        st = lib.kcg_gemm_host_staged(ctypes.byref(d), a_host.data_ptr(),
+                                      b_host.data_ptr() if b_host is not None else None, c_host.data_ptr(),
                                       a_dev.data_ptr(), b_dev.data_ptr(), c_dev.data_ptr(),
                                       ws.data_ptr() if ws is not None else None, ws_bytes, chunks,
                                       torch.cuda.current_stream(dev).cuda_stream)

@@ -39,6 +39,22 @@ def test_staged_equals_single_launch(m, n, k, dtype, b_col_major, chunks):
         assert torch.equal(c_d, want)
 
 
+def test_staged_with_b_already_on_the_device():
+    """hB = NULL: only A moves in and C out; B is whatever the device array holds."""
+    from kernelcodegen_b200 import ops
+    dev = torch.device("cuda:0")
+    m, n, k = 4300, 2056, 512
+    a, b = _mk((m, k), torch.bfloat16, 7, dev), _mk((k, n), torch.bfloat16, 8, dev)
+    want = ops.matmul(a, b, relu=True)
+    a_h = a.cpu().pin_memory()
+    c_h = torch.full((m, n), float("nan"), dtype=torch.bfloat16).pin_memory()
+    a_d, c_d = torch.zeros_like(a), torch.zeros_like(want)
+    ops.matmul_host(a_h, None, c_h, a_d, b, c_d, relu=True)
+    torch.cuda.synchronize()
+    assert torch.equal(c_h, want.cpu()) and torch.equal(c_d, want)
+    assert ops.last_device_status() == 0
+
+
 def test_staged_pageable_host_memory_and_oracle():
     from kernelcodegen_b200 import ops
     from oracle import oracle
