@@ -9,8 +9,11 @@
 //   warp 0      TMA producer : global -> 128B-swizzled shared memory, STAGES-deep mbarrier ring
 //   warp 1      UMMA issuer  : tcgen05.mma 128 x BN x (32 bytes of K), accumulators in TMEM,
 //                              two accumulator buffers so tile i+1 starts while tile i drains
-//   warps 2..5  epilogue     : tcgen05.ld -> ReLU -> (bf16 pack) -> global stores
-//                              (and, for the fused all-gather, the same stores to peer GPUs)
+//   warps 2..5  epilogue of the tiles in accumulator buffer 0 } tcgen05.ld -> ReLU -> (bf16 pack)
+//   warps 6..9  epilogue of the tiles in accumulator buffer 1 } -> global stores (and, for the
+//                              fused all-gather, the same stores to peer GPUs).  Two groups, so
+//                              that a drain may take two main loops: with seven peer copies to
+//                              write, one group of four warps was slower than the main loop.
 //
 // The grid is persistent (one CTA per SM); tiles are walked in groups of `group_m` row blocks
 // so that concurrently running CTAs share A and B panels in L2.
@@ -35,7 +38,8 @@ constexpr size_t STATIC_SCRATCH_BYTES = KCG_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;         // CTA-pair kernel: producer, issuer, 4 epilogue warps
+constexpr int GEMM1_THREADS = 320;        // single-CTA kernel: producer, issuer, 2 x 4 epilogue warps
 constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in limit per CTA
 
 struct GemmParams {
@@ -112,7 +116,7 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = NOPS * (A_BYTES + B_BYTES);
   static constexpr int CTRL_BYTES = 1024;            // barriers, TMEM pointer, abort flag
-  static constexpr int EPI_BYTES = 4 * 4096;         // one 32-row x 128-byte staging slab per epilogue warp
+  static constexpr int EPI_BYTES = 8 * 4096;         // one 32-row x 128-byte staging slab per epilogue warp
   static constexpr int MAX_STAGES = (SMEM_LIMIT - CTRL_BYTES - EPI_BYTES - 1024) / STAGE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;           // two accumulator buffers (256 or 512)
 };
@@ -270,7 +274,7 @@ __device__ __forceinline__ void write_partial(uint32_t t_row, float* dst, int la
 }
 
 template <int KIND, int BN, int STAGES, bool B_KMAJOR, typename OutT>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM1_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
             const GemmParams p) {
@@ -464,15 +468,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
   } else {
-    // ------------------------------- epilogue (4 warps) --------------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    uint8_t* epi_stage = ctrl + Cfg::CTRL_BYTES + q * 4096;  // this warp's 32 x 128 B slab
+    // ------------------------------- epilogue (2 groups of 4 warps) --------------------------
+    const int q = warp & 3;               // TMEM lane quarter this warp may read
+    const int grp = (warp - 2) >> 2;      // group g drains the tiles that land in accumulator buffer g
+    uint8_t* epi_stage = ctrl + Cfg::CTRL_BYTES + (grp * 4 + q) * 4096;  // this warp's 32 x 128 B slab
     int local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      const int acc = local & 1;
+      if (acc != grp) continue;
       int mb, nb;
       tile_coord(t, mb, nb);
-      const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE,
                      p.spin);
@@ -902,7 +908,7 @@ kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.blockDim = dim3(GEMM1_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cfg.attrs = attr;
