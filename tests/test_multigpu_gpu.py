@@ -49,6 +49,15 @@ def _worker(rank, world, port, out_dir):
     got = cm.tensor.float().cpu().numpy()
     want = oracle.matmul_relu(a.float().numpy(), b.float().numpy())
     err = float(np.abs(got - want).max() / np.abs(want).max())
+    # the same with single CTAs (the kernel long launches use: two epilogue warp groups)
+    cm.tensor.fill_(-1.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    ops.matmul_relu(a[lo:hi].to(dev), b.to(dev), out=cm.tensor[lo:hi], peers=cm.peer_row_ptrs(lo), cta_group=1)
+    dist.all_reduce(token)
+    torch.cuda.synchronize()
+    got = cm.tensor.float().cpu().numpy()
+    err = max(err, float(np.abs(got - want).max() / np.abs(want).max()))
     # the same all-gather through the host-buffer entry: strips computed from chunked copies
     # must land in both ranks' copies of C and in this rank's host block
     cm.tensor.fill_(-1.0)
