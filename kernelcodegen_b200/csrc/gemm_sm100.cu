@@ -12,8 +12,8 @@
 //   warps 2..5  epilogue of the tiles in accumulator buffer 0 } tcgen05.ld -> ReLU -> (bf16 pack)
 //   warps 6..9  epilogue of the tiles in accumulator buffer 1 } -> global stores (and, for the
 //                              fused all-gather, the same stores to peer GPUs).  Two groups, so
-//                              that a drain may take two main loops: with seven peer copies to
-//                              write, one group of four warps was slower than the main loop.
+//                              that a drain (up to eight copies of the tile) may take as long as
+//                              two main loops before it holds up the issuer.
 //
 // The grid is persistent (one CTA per SM); tiles are walked in groups of `group_m` row blocks
 // so that concurrently running CTAs share A and B panels in L2.
