@@ -125,6 +125,13 @@ size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d);
  * covers for this descriptor on a B200's 74 CTA pairs; 0 = the launch has no shared-K tail. */
 int kcg_gemm_shared_k_tiles(const kcg_gemm_desc* d);
 
+/* Introspection for tests (no counterpart in the reference): the shared-K plan for `tiles` pair
+ * tiles of `num_kb` k-blocks on `pairs` CTA pairs; out5 = {tail tiles, ranges, k-block positions
+ * per range, positions per tile (>= num_kb: the surplus is padding), most contributors per tile};
+ * all zero when the launch has no shared-K tail.  Range u covers positions [u*share, (u+1)*share)
+ * of the tail tiles laid end to end, `span` positions per tile. */
+void kcg_gemm_shared_k_plan(int32_t tiles, int32_t num_kb, int32_t pairs, int32_t tile_n, int32_t* out5);
+
 /* Replaces: launch of `<graph>::kernel0(A, B, C)` emitted by CUDAGen
  * (src/Backend/CUDA.cc:773-857) for the scheduled Matmul func, with Relu fused. */
 kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,

@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "kcg_gemm_workspace_bytes",
     "kcg_fmha_workspace_bytes",
     "kcg_gemm_shared_k_tiles",
+    "kcg_gemm_shared_k_plan",
     "kcg_gemm_launch",
     "kcg_gemm_launch_static",
     "kcg_fmha_fwd_launch",
@@ -107,6 +108,8 @@ def load() -> ctypes.CDLL:
     lib.kcg_fmha_workspace_bytes.restype = c_size_t
     lib.kcg_gemm_shared_k_tiles.restype = c_int
     lib.kcg_gemm_shared_k_tiles.argtypes = [POINTER(GemmDesc)]
+    lib.kcg_gemm_shared_k_plan.restype = None
+    lib.kcg_gemm_shared_k_plan.argtypes = [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32)]
     lib.kcg_fmha_workspace_bytes.argtypes = [POINTER(FmhaDesc)]
     lib.kcg_gemm_launch.restype = c_int
     lib.kcg_gemm_launch.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]

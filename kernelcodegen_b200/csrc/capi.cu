@@ -125,6 +125,9 @@ extern "C" {
 size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d) { return gemm_workspace_impl(d); }
 size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d) { return fmha_workspace_impl(d); }
 int kcg_gemm_shared_k_tiles(const kcg_gemm_desc* d) { return gemm_shared_k_tiles_impl(d); }
+void kcg_gemm_shared_k_plan(int32_t tiles, int32_t num_kb, int32_t pairs, int32_t tile_n, int32_t* out5) {
+  if (out5 && tiles > 0 && num_kb > 0 && pairs > 0) gemm_shared_k_plan_impl(tiles, num_kb, pairs, tile_n, out5);
+}
 
 kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                              void* workspace, size_t workspace_bytes, void* stream) {

@@ -41,6 +41,7 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
 size_t gemm_workspace_impl(const kcg_gemm_desc* d);
 int gemm_shared_k_tiles_impl(const kcg_gemm_desc* d);
 void gemm_reset_shared_k_counters();
+void gemm_shared_k_plan_impl(int tiles, int num_kb, int pairs, int bn, int* out);
 kcg_status_t transpose_launch_impl(int64_t batch, int64_t rows, int64_t cols, int dtype, const void* x, void* y,
                                    cudaStream_t stream);
 kcg_status_t gemm_launch_static_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,

@@ -1019,6 +1019,16 @@ static void resolve_variant(const kcg_gemm_desc* d, int* bn, bool* pair_mode) {
   *pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM && small_job);
 }
 
+// The plan itself, for tests: out = {tail tiles, units, share, span, max contributors per tile}.
+void gemm_shared_k_plan_impl(int tiles, int num_kb, int pairs, int bn, int* out) {
+  const SkPlan pl = plan_shared_k(tiles, num_kb, pairs, bn);
+  out[0] = pl.tiles;
+  out[1] = pl.units;
+  out[2] = pl.share;
+  out[3] = pl.span;
+  out[4] = pl.maxc;
+}
+
 // Zeroes the arrival counters on the current device (after a launch that ended on a bounded wait;
 // the device is idle when this is called).
 void gemm_reset_shared_k_counters() {

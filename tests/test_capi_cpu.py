@@ -146,3 +146,42 @@ def test_product_package_does_not_touch_the_oracle():
     for path in list(pkg.rglob("*.py")) + list(pkg.rglob("*.cu")) + list(pkg.rglob("*.cuh")):
         text = path.read_text()
         assert "oracle" not in text.lower(), f"{path} mentions the oracle"
+
+
+def test_shared_k_plan_covers_every_k_block_once(native_lib):
+    """Walks the plan the way the kernel's work iterator does (range u = positions [u*share,
+    (u+1)*share) of the tail tiles laid end to end, `span` positions per tile, positions past
+    num_kb are padding) and checks that every k-block of every tail tile is covered exactly once,
+    that no range is longer than a tile, and that no tile has more contributors than announced."""
+    out = (ctypes.c_int32 * 5)()
+    planned = 0
+    for pairs in (74, 66, 9):
+        for num_kb in (8, 9, 15, 16, 31, 32, 33, 64, 100, 512):
+            for tiles in range(1, 3 * pairs + 1):
+                for i in range(5):
+                    out[i] = 0
+                native_lib.kcg_gemm_shared_k_plan(tiles, num_kb, pairs, 128, out)
+                tail, units, share, span, maxc = list(out)
+                if tail == 0:
+                    continue
+                planned += 1
+                assert tail == tiles % pairs and 0 < units <= pairs and span >= num_kb and share <= num_kb
+                cover = [[0] * num_kb for _ in range(tail)]
+                contrib = [set() for _ in range(tail)]
+                for u in range(units):
+                    lin0, lin1 = min(tail * span, u * share), min(tail * span, (u + 1) * share)
+                    while lin0 < lin1:
+                        ti, off = divmod(lin0, span)
+                        end = min(span, off + (lin1 - lin0))
+                        lin0 += end - off
+                        if off < num_kb:
+                            for kb in range(off, min(num_kb, end)):
+                                cover[ti][kb] += 1
+                            contrib[ti].add(u)
+                assert all(c == 1 for row in cover for c in row), (tiles, num_kb, pairs)
+                for ti in range(tail):
+                    first = (ti * span) // share
+                    last = min(units - 1, (ti * span + num_kb - 1) // share)
+                    assert contrib[ti] == set(range(first, last + 1))      # what the epilogue counts on
+                    assert len(contrib[ti]) <= maxc
+    assert planned > 100
