@@ -157,6 +157,26 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     *abort_flag = 0;
     mbar_fence_init();
+    // This thread is also the TMA producer: the Q tiles and the first K / V block go out now and
+    // are in flight while TMEM is allocated and the CTA synchronises.
+    if (n_kv > 0) {
+      // fp32 inputs, head dimension 128: the bf16 copies come from the launch just before this one
+      if (p.after_cast) griddep_wait();
+#pragma unroll
+      for (int t = 0; t < QTILES; ++t) {
+        if (n_kv_t[t] == 0) continue;
+        mbar_expect_tx(bar_q + 8 * t, TILE);
+#pragma unroll
+        for (int dp = 0; dp < DPANELS; ++dp)
+          tma_load_3d(sQ + t * TILE + dp * PANEL, &tmQ, bar_q + 8 * t, dp * PW, q0 + t * BQ, bh);
+      }
+      mbar_expect_tx(bar_kfull, TILE);
+#pragma unroll
+      for (int dp = 0; dp < DPANELS; ++dp) tma_load_3d(sK + dp * PANEL, &tmK, bar_kfull, dp * PW, 0, bh);
+      mbar_expect_tx(bar_vfull, TILE);
+#pragma unroll
+      for (int dp = 0; dp < DPANELS; ++dp) tma_load_3d(sV + dp * PANEL, &tmV, bar_vfull, dp * PW, 0, bh);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_holder), Cfg::TMEM_COLS);
@@ -171,18 +191,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     reg_dealloc_56();
     if (warp == 0 && lane == 0 && n_kv > 0) {
       // ------------------------------- TMA producer -----------------------------------------
-      // fp32 inputs: the bf16 copies come from the launch just before this one (no-op otherwise)
-      if (p.after_cast) griddep_wait();
-#pragma unroll
-      for (int t = 0; t < QTILES; ++t) {
-        if (n_kv_t[t] == 0) continue;
-        mbar_expect_tx(bar_q + 8 * t, TILE);
-#pragma unroll
-        for (int dp = 0; dp < DPANELS; ++dp)
-          tma_load_3d(sQ + t * TILE + dp * PANEL, &tmQ, bar_q + 8 * t, dp * PW, q0 + t * BQ, bh);
-      }
+      // (block 0 and the Q tiles were issued before the CTA-wide synchronisation above)
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
+      for (int j = 1; j < n_kv && ok; ++j) {
         const int b = j & 1;
         const uint32_t par = ((j >> 1) & 1u) ^ 1u;
         ok = mbar_wait(bar_kempty + 8 * b, par, abort_flag, p.status, DEV_TIMEOUT_PRODUCER, p.spin);
