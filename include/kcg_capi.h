@@ -83,7 +83,7 @@ typedef struct kcg_gemm_desc {
   int32_t group_m;
   /* Fused all-gather (optional): when n_peers > 0 every finished C tile is also stored to
    * peer_c[i] + the same offset, i = 0..n_peers-1 (peer-mapped device pointers of the other
-   * ranks' C buffers, already offset to this rank's row block). Plain stores, no multicast. */
+   * ranks' C buffers, already offset to this rank's row block). Plain unicast stores. */
   int32_t n_peers;
   /* 1: one CTA per 128 x tile_n tile.  2: CTA pairs (tcgen05 cta_group::2) share a
    * 256 x tile_n tile, each CTA loading half of the B tile.  0: library default (pairs for launches

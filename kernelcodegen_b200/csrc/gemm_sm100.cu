@@ -510,7 +510,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // Protocol: `full` barriers live in the leader (it expects the bytes of both CTAs' TMA loads,
 // the peer's loads signal it through its cluster address); `empty` and `tmem_full` barriers are
 // per CTA and the leader commits to both; `tmem_empty` lives in the leader and collects the 256
-// epilogue threads of both CTAs.  No multicast anywhere.
+// epilogue threads of both CTAs.  Every TMA load is a plain per-CTA load.
 template <int KIND, int BN>
 struct PairCfg {
   static constexpr int ES = (KIND == 0) ? 2 : 4;

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, never with cluster multicast), tcgen05
+// mbarrier, TMA (plain per-CTA cp.async.bulk.tensor loads only), tcgen05
 // (TMEM allocation, UMMA issue/commit, TMEM loads) and the proxy fences between them.
 // Every wait is bounded: a wait that runs out records a code in a status word and
 // returns false so the kernel can unwind (free TMEM, return) instead of spinning.
@@ -112,7 +112,7 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
   return old;
 }
 
-// ---- TMA loads (per-CTA, no multicast) -------------------------------------------------------
+// ---- TMA loads (each CTA loads its own tiles) ------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int x, int y) {
   asm volatile(
@@ -293,7 +293,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load issued by one CTA of a pair; the completion bytes go to `bar`, a shared::cluster
-// address that may name the leader CTA's barrier.  No multicast: each CTA loads its own tile.
+// address that may name the leader CTA's barrier.  Each CTA loads its own tile.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                                  int x, int y) {
   asm volatile(

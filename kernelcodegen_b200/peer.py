@@ -3,7 +3,7 @@
 Every rank allocates its full C buffer through `kcg_peer_alloc`, the 64-byte handles travel
 over `torch.distributed` (any backend: they are plain bytes), and each rank maps the others'
 buffers with `kcg_peer_open`.  The GEMM epilogue then stores each finished tile into the local
-buffer and into every peer's buffer (plain stores over NVLink; no multicast, no collective
+buffer and into every peer's buffer (plain unicast stores over NVLink; no collective
 kernel), so that when all ranks' kernels have finished every rank holds the whole of C.
 """
 from __future__ import annotations
