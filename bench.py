@@ -3,23 +3,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --case <name> [--iters I]        # one small case, for profiler captures
 
 One JSON line on stdout (rank 0).  The workload of `value` is the same at every N so that the
 per-N values form a strong-scaling curve: the large bf16 matmul+ReLU (M=N=K=32768, inputs
 N(0, 0.02) in bf16, fp32 accumulate, bf16 output), A and C sharded by row blocks over the ranks,
-every finished C tile stored into all ranks' copies of C by the GEMM epilogue itself (fused
-all-gather over NVLink peer memory), one step = one full C on every rank.
-At N=1 the line also carries the other configurations (`others`): the fp32-contract
-4096x1024x2048 matmul+ReLU (3xTF32), the fp32 square sweep, and the two FMHA configs; at N>1
-it carries the bf16 causal FMHA sharded by batch*head.
+every finished C tile delivered to all ranks' copies of C by the GEMM epilogue itself (fused
+all-gather: one multicast store through the NVSwitch, or unicast peer stores), completion by
+per-rank flags and a bounded device-side wait; one step = one full C on every rank.
+The configuration the metric string leads with, the fp32-contract 4096x1024x2048 matmul+ReLU,
+has its own first-class block `c1` at N=1 (device-timed, end to end from host buffers, CPU
+baseline on the full nest, parity against the CPU nest); the remaining configurations ride in
+`others` (N=1: the fp32 square sweep, both FMHA configs, the un-fused attention graph, Softmax,
+Transpose; N>1: the bf16 causal FMHA sharded by batch*head).
 
 `--impl reference` times the CPU restatement of the reference's loop nest (the reference has
-no executable CPU or GPU path of its own in this environment) on the host cores.
+no executable CPU or GPU path of its own in this environment) on all host threads.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -33,10 +38,15 @@ if str(ROOT) not in sys.path:
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the bf16 GEMM kernel, from the
-# ncu capture summarised in profiles/ (8192^3 case) scaled to 32768^3 by tiles processed.
-# (profiles/gemm_bf16_8192_ncu.md: 1.011 GB read + 0.130 GB written.)
-GEMM_BF16_DRAM_BYTES_PER_LAUNCH_8192 = 1.141e9
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each) of ONE launch of
+# the dominant kernel on a case small enough to capture; scaled to the bench's launch by the tiles
+# (x k-blocks) processed.  None = not captured.
+DRAM_BYTES_GEMM_BF16 = {"shape": (16384, 16384, 16384), "bytes": None}
+DRAM_BYTES_GEMM_BF16_8192 = {"shape": (8192, 8192, 8192), "bytes": 1.141e9}
+DRAM_BYTES_C1 = 60.6e6          # 3xTF32 GEMM 4096x2048x1024 incl. the residual arrays it reads
+
+METRIC = "TFLOP/s & % tensor roofline: matmul+ReLU 4096x1024x2048, FMHA; 1/2/4/8 GPU"
+LARGE = 32768
 
 
 def load_peaks():
@@ -50,6 +60,15 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def host_threads() -> int:
+    """Host threads this process may use.  (Launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1 to their children; the CPU legs therefore pass an explicit count.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 # ------------------------------------------------------------------------------------------------
 # clocks
 # ------------------------------------------------------------------------------------------------
@@ -58,24 +77,27 @@ class ClockSampler:
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_ms: int = 50):
         self.gpu_index = gpu_index
+        self.period_ms = period_ms
         self.proc = None
-        self.path = f"/tmp/kcg_clocks_{os.getpid()}.csv"
+        self.path = f"/tmp/kcg_clocks_{os.getpid()}_{time.monotonic_ns()}.csv"
 
     def start(self):
         try:
             self.fh = open(self.path, "w")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
                  "-i", str(self.gpu_index)], stdout=self.fh, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+        return self
 
     def stop(self):
+        empty = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        time.sleep(0.15)
+            return empty
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -102,7 +124,7 @@ class ClockSampler:
         except OSError:
             pass
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return empty
         # "under load": samples whose power is above half of the highest seen
         hi = max(power)
         loaded = [c for c, p in zip(sm, power) if p >= 0.5 * hi] or sm
@@ -110,10 +132,23 @@ class ClockSampler:
                 "samples": len(sm), "power_w_max": hi}
 
 
+def with_clocks(entry: dict, clocks: dict) -> dict:
+    """Attach a clock sample to a result; `ms_x_mhz` (time x median SM MHz under load) compares
+    runs taken at different clocks."""
+    entry["clocks"] = clocks
+    if clocks.get("sm_mhz") and entry.get("ms") is not None:
+        entry["ms_x_mhz"] = entry["ms"] * clocks["sm_mhz"]
+    return entry
+
+
 # ------------------------------------------------------------------------------------------------
-# reference arm: the CPU restatement of the reference's nest, all host threads
+# CPU legs: the restatement of the reference's nest on the host cores
 # ------------------------------------------------------------------------------------------------
-LARGE = 32768
+def _bf16_round(x):
+    import numpy as np
+
+    u = x.view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
 
 
 def cpu_sample_inputs(rows: int, cols: int, k: int):
@@ -122,11 +157,7 @@ def cpu_sample_inputs(rows: int, cols: int, k: int):
     rng = np.random.default_rng(40)
     a = (rng.standard_normal((rows, k)) * 0.02).astype(np.float32)
     b = (rng.standard_normal((k, cols)) * 0.02).astype(np.float32)
-    # round to bf16 (the workload's input type), keep as float for the fp32 nest
-    def bf16(x):
-        u = x.view(np.uint32)
-        return ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
-    return bf16(a), bf16(b)
+    return _bf16_round(a), _bf16_round(b)      # bf16 values (the workload's input type) held as floats
 
 
 def cpu_time_sample(rows: int, cols: int, k: int, threads: int) -> float:
@@ -134,27 +165,41 @@ def cpu_time_sample(rows: int, cols: int, k: int, threads: int) -> float:
 
     a, b = cpu_sample_inputs(rows, cols, k)
     t0 = time.perf_counter()
-    oracle.matmul_relu(a, b, threads=threads)
+    oracle.matmul_relu(a, b, threads=threads if threads > 1 else 1)
     return time.perf_counter() - t0
 
 
-def cpu_baseline(target_s: float = 12.0):
+def cpu_baseline(target_s: float = 10.0):
     """TFLOP/s of the reference nest on the host cores, on a bounded sample of the large GEMM:
     `rows` rows x 2048 columns of C at the full K = 32768."""
     from oracle import oracle
 
     oracle.build()
-    threads = oracle.max_threads()
+    threads = host_threads()
     cols, k = 2048, LARGE
     rows = max(1, threads // 16)
-    t = cpu_time_sample(rows, cols, k, 0)
+    t = cpu_time_sample(rows, cols, k, threads)
     if t < target_s / 2:
         rows = max(rows, int(rows * target_s / max(t, 1e-3)))
         rows = min(rows, 4096)
-        t = cpu_time_sample(rows, cols, k, 0)
+        t = cpu_time_sample(rows, cols, k, threads)
     flops = 2.0 * rows * cols * k
     return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
             "sample": f"{rows} rows x {cols} cols of C at K={k} (bf16-rounded inputs, fp32 nest), {t:.1f} s"}
+
+
+def cpu_baseline_c1(a_np, b_np):
+    """The whole 4096x1024x2048 nest + ReLU on all host threads; returns (record, C)."""
+    from oracle import oracle
+
+    threads = host_threads()
+    t0 = time.perf_counter()
+    c = oracle.matmul_relu(a_np, b_np, threads=threads if threads > 1 else 1)
+    t = time.perf_counter() - t0
+    m, k = a_np.shape
+    n = b_np.shape[1]
+    return {"value": 2.0 * m * n * k / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"the full {m}x{k}x{n} fp32 nest + ReLU, {t:.1f} s"}, c
 
 
 def run_reference(args):
@@ -164,15 +209,15 @@ def run_reference(args):
     from oracle import oracle
 
     oracle.build()
-    threads = oracle.max_threads()
+    threads = host_threads()
     cols, k = 2048, LARGE
     rows = max(1, threads // 16)
-    t = cpu_time_sample(rows, cols, k, 0)  # calibration (also a warm-up of the thread pool)
+    t = cpu_time_sample(rows, cols, k, threads)  # calibration (also a warm-up of the thread pool)
     per_step_target = 4.0
     rows = max(1, min(4096, int(rows * per_step_target / max(t, 1e-3))))
     for _ in range(args.warmup):
-        cpu_time_sample(rows, cols, k, 0)
-    times = [cpu_time_sample(rows, cols, k, 0) for _ in range(args.steps)]
+        cpu_time_sample(rows, cols, k, threads)
+    times = [cpu_time_sample(rows, cols, k, threads) for _ in range(args.steps)]
     total = sum(times)
     flops = 2.0 * rows * cols * k * args.steps
     value = flops / total / 1e12
@@ -184,6 +229,7 @@ def run_reference(args):
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "parity": "partial: the CPU nest is pinned only by this repository's own float64 fixtures (the reference holds no vectors)",
         "note": "the reference has no CPU executor and cannot be built here (needs LLVM/MLIR 15); this is the "
                 "C restatement of its loop nest on all host threads",
     }
@@ -191,23 +237,41 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------------
-# our arm
+# timing helpers
 # ------------------------------------------------------------------------------------------------
-METRIC = "TFLOP/s & % tensor roofline: matmul+ReLU 4096x1024x2048, FMHA; 1/2/4/8 GPU"
+def workload_config(n, completion=None, store=None, preheat_s=None):
+    cfg = {"workload": "large bf16 matmul+ReLU M=N=K=32768 (bf16 in N(0,0.02), fp32 accumulate, bf16 out), "
+                       "A/C sharded by row blocks, C all-gathered by the GEMM epilogue's own stores",
+           "M": LARGE, "N": LARGE, "K": LARGE, "parallelism": f"row-block x{n}",
+           "cache": "inputs (2 GiB per operand) are larger than L2 (126 MB); no flush needed"}
+    if completion:
+        cfg["completion"] = completion
+    if store:
+        cfg["allgather_store"] = store
+    if preheat_s is not None:
+        cfg["preheat"] = (f"untimed warm-up steps continue until {preheat_s:g} s of work have run, so that the timed steps "
+                          "see the steady power-capped clocks at every N")
+    return cfg
 
 
-def workload_config(n):
-    return {"workload": "large bf16 matmul+ReLU M=N=K=32768 (bf16 in N(0,0.02), fp32 accumulate, bf16 out), "
-                        "A/C sharded by row blocks, C all-gathered by peer stores in the GEMM epilogue",
-            "M": LARGE, "N": LARGE, "K": LARGE, "parallelism": f"row-block x{n}",
-            "cache": "inputs (2 GiB per operand) are larger than L2 (126 MB); no flush needed"}
-
-
-def time_steps(fn, steps, warmup, torch, dist=None):
-    """W warm-ups, then K steps between barrier+synchronize, CUDA events on the current stream;
-    returns max-over-ranks milliseconds for the K steps."""
+def time_steps(fn, steps, warmup, torch, dist=None, drain=None, preheat_s=0.0):
+    """W warm-ups (more, until `preheat_s` seconds have run), then K steps between
+    barrier+synchronize, CUDA events on the current stream; `drain` (if any) runs inside the timed
+    region after the last step.  Returns max-over-ranks milliseconds for the K steps."""
+    t0 = time.perf_counter()
     for _ in range(warmup):
         fn()
+    while preheat_s > 0:
+        torch.cuda.synchronize()
+        more = torch.tensor([1.0 if time.perf_counter() - t0 < preheat_s else 0.0], device="cuda")
+        if dist is not None:
+            dist.all_reduce(more, op=dist.ReduceOp.MIN)      # all ranks leave the warm-up together
+        if more.item() == 0.0:
+            break
+        for _ in range(4):
+            fn()
+    if drain is not None:
+        drain()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
@@ -217,6 +281,8 @@ def time_steps(fn, steps, warmup, torch, dist=None):
     e0.record()
     for _ in range(steps):
         fn()
+    if drain is not None:
+        drain()
     e1.record()
     torch.cuda.synchronize()
     if dist is not None:
@@ -230,15 +296,11 @@ def time_steps(fn, steps, warmup, torch, dist=None):
     return ms
 
 
-def flush_l2(torch, buf):
-    buf.zero_()
-
-
 def time_flushed(fn, iters, torch, flush_buf):
     """Per-launch time (median) with an L2 flush (a write larger than L2) between timed launches."""
     times = []
     for _ in range(iters):
-        flush_l2(torch, flush_buf)
+        flush_buf.zero_()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -281,84 +343,67 @@ def settle(torch, seconds=1.0):
     time.sleep(seconds)
 
 
-def others_single_gpu(torch, dev, peaks, ops):
-    """The other configurations of the metric, 1 GPU, CUDA-event timed, L2 flushed between
-    launches where the working set fits L2; one second of idle time before each (see settle)."""
-    res = []
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    settle(torch)
-    tf32_peak = measure_tf32_peak(torch, dev)
-    x3_peak = tf32_peak / 3.0
+def uniform(torch, dev, shape, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return torch.rand(shape, generator=g, device=dev) * 2 - 1
 
-    def uniform(shape, seed):
-        g = torch.Generator(device=dev).manual_seed(seed)
-        return torch.rand(shape, generator=g, device=dev) * 2 - 1
 
-    # fuse_matmul_relu fp32 4096x1024x2048
-    a, b = uniform((4096, 1024), 0), uniform((1024, 2048), 1)
-    c = torch.empty((4096, 2048), device=dev)
+# ------------------------------------------------------------------------------------------------
+# config 1: fuse_matmul_relu fp32 4096x1024x2048, first class
+# ------------------------------------------------------------------------------------------------
+def c1_block(torch, dev, ops, x3_peak, tf32_peak, flush_buf, gpu_index, with_cpu=True):
+    import numpy as np
+
+    M, K, N = 4096, 1024, 2048
+    a, b = uniform(torch, dev, (M, K), 0), uniform(torch, dev, (K, N), 1)
+    c = torch.empty((M, N), device=dev)
     fn = lambda: ops.matmul_relu(a, b, out=c)
     for _ in range(3):
         fn()
     settle(torch)
+    smp = ClockSampler(gpu_index).start()
     ms_cold = time_flushed(fn, 20, torch, flush_buf)
     ms_warm = time_steps(fn, 20, 3, torch) / 20
-    fl = 2.0 * 4096 * 2048 * 1024
-    res.append({"workload": "fuse_matmul_relu fp32 4096x1024x2048 (3xTF32, incl. hi/lo split pass)",
-                "tflops": fl / ms_cold / 1e9, "ms": ms_cold, "tflops_warm_l2": fl / ms_warm / 1e9, "ms_warm_l2": ms_warm,
-                "roofline": {"bound": "tensor", "achieved": fl / ms_cold / 1e9, "peak": x3_peak, "unit": "TFLOP/s",
-                             "frac": fl / ms_cold / 1e9 / x3_peak,
-                             "peak_def": f"cuBLAS TF32 8192^3 measured live ({tf32_peak:.0f}) / 3"},
-                "timing": "L2 flushed between launches (cold, median of 20); warm = 20 back-to-back; 1 s idle before"})
-    # fp32 square sweep
-    for i, n in enumerate((1024, 2048, 4096, 8192)):
-        a, b = uniform((n, n), 10 + i), uniform((n, n), 10 + i + 100)
-        c = torch.empty((n, n), device=dev)
-        fn = lambda: ops.matmul_relu(a, b, out=c)
-        for _ in range(3):
-            fn()
-        settle(torch)
-        ms = time_flushed(fn, 10, torch, flush_buf)
-        fl = 2.0 * n ** 3
-        res.append({"workload": f"fp32 matmul+ReLU {n}^3 (3xTF32)", "tflops": fl / ms / 1e9, "ms": ms,
-                    "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": x3_peak, "unit": "TFLOP/s",
-                                 "frac": fl / ms / 1e9 / x3_peak}})
-    del a, b, c
-    # FMHA fp32 in/out non-causal B4 H16 S1024 D64
-    g = torch.Generator(device=dev)
-    qkv = []
-    for seed in (20, 21, 22):
-        g.manual_seed(seed)
-        qkv.append(torch.randn((4, 16, 1024, 64), generator=g, device=dev))
-    o = torch.empty_like(qkv[0])
-    fn = lambda: ops.fmha(qkv[0], qkv[1], qkv[2], scale=0.125, out=o)
-    for _ in range(3):
-        fn()
-    settle(torch)
-    ms = time_flushed(fn, 20, torch, flush_buf)
-    fl = 4.0 * 4 * 16 * 1024 * 1024 * 64
-    res.append({"workload": "FMHA fp32-in/out non-causal B4 H16 S1024 D64 (both contractions TF32 on the fp32 tiles, no conversion pass)",
-                "tflops": fl / ms / 1e9, "ms": ms, "tolerance": "5e-3 (TF32 internals)",
-                "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": tf32_peak, "unit": "TFLOP/s",
-                             "frac": fl / ms / 1e9 / tf32_peak,
-                             "peak_def": "cuBLAS TF32 8192^3 measured live"}})
-    res.append(fmha_long(torch, dev, peaks, ops, 0, 256))
-    del qkv, o
-    # Transpose (HBM-bound): 8192 x 8192 fp32, 256 MiB in + 256 MiB out, larger than L2
-    x = torch.randn((8192, 8192), device=dev)
-    for _ in range(3):
-        y = ops.transpose(x)
-    settle(torch)
-    ms = time_steps(lambda: ops.transpose(x), 10, 0, torch, None) / 10
-    nbytes = 2.0 * x.numel() * 4
-    res.append({"workload": "Transpose 8192x8192 fp32 (read once, write once)", "gbs": nbytes / ms / 1e6, "ms": ms,
-                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"]}})
-    del x, y
-    return res, tf32_peak
+    clocks = smp.stop()
+    fl = 2.0 * M * N * K
+    algo_bytes = 4.0 * (M * K + K * N + M * N)
+    blk = {"workload": "fuse_matmul_relu fp32 4096x1024x2048: C = ReLU(A.B), uniform[-1,1], 3xTF32 on tcgen05 "
+                       "(the residual pass is inside the timed region)",
+           "value": fl / ms_cold / 1e9, "unit": "TFLOP/s", "ms": ms_cold, "dtype": "f32 (3xTF32 split, fp32 accumulate)",
+           "value_warm_l2": fl / ms_warm / 1e9, "ms_warm_l2": ms_warm,
+           "timing": "CUDA events; L2 flushed (256 MiB write) between launches, median of 20; warm = 20 back to back; 1 s idle before",
+           "roofline": {"bound": "tensor", "achieved": fl / ms_cold / 1e9, "peak": x3_peak, "unit": "TFLOP/s",
+                        "frac": fl / ms_cold / 1e9 / x3_peak, "traffic": DRAM_BYTES_C1, "algorithmic_bytes": algo_bytes,
+                        "peak_def": f"cuBLAS TF32 8192^3 measured live ({tf32_peak:.0f}) / 3"}}
+    with_clocks(blk, clocks)
+    # end to end from host buffers: pinned A, B in, C out, every step, through kcg_gemm_host_staged
+    a_h, b_h = a.cpu().pin_memory(), b.cpu().pin_memory()
+    c_h = torch.empty((M, N), dtype=torch.float32).pin_memory()
+    a_d, b_d, c_d = torch.empty_like(a), torch.empty_like(b), torch.empty_like(c)
+    e2e_fn = lambda: ops.matmul_host(a_h, b_h, c_h, a_d, b_d, c_d, relu=True)
+    e2e_ms = time_steps(e2e_fn, 10, 3, torch) / 10
+    blk["e2e"] = {"value": fl / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                  "h2d_bytes_per_step": 4 * (M * K + K * N), "d2h_bytes_per_step": 4 * M * N,
+                  "note": "pinned host A, B -> device, GEMM, C -> host, every step (kcg_gemm_host_staged); PCIe-bound: "
+                          "56 MiB per step against 80 us of math"}
+    # parity against the CPU nest (the checker), and the CPU baseline on the whole nest
+    a_np, b_np = a_h.numpy(), b_h.numpy()
+    got = c_h.numpy()
+    if with_cpu:
+        try:
+            rec, want = cpu_baseline_c1(a_np, b_np)
+            blk["cpu_baseline"] = rec
+            blk["parity"] = {"max_rel_err": float(np.abs(got - want).max() / np.abs(want).max()), "bar": 1e-4,
+                             "against": "the full fp32 nest + ReLU on the CPU, same input bits", "pinned": False}
+        except Exception as ex:
+            blk["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+    return blk
 
 
-def fmha_long(torch, dev, peaks, ops, bh_lo, bh_hi, dist=None, steps=5):
+# ------------------------------------------------------------------------------------------------
+# the other configurations (1 GPU)
+# ------------------------------------------------------------------------------------------------
+def fmha_long(torch, dev, peaks, ops, bh_lo, bh_hi, gpu_index, dist=None, steps=5):
     """bf16 causal B8 H32 S8192 D128, the (batch*head) range [bh_lo, bh_hi) on this rank."""
     n = bh_hi - bh_lo
     g = torch.Generator(device=dev)
@@ -375,25 +420,197 @@ def fmha_long(torch, dev, peaks, ops, bh_lo, bh_hi, dist=None, steps=5):
     for _ in range(3):
         fn()
     batches = []
+    smp = ClockSampler(gpu_index).start() if gpu_index is not None else None
     for _ in range(3):
         settle(torch)
         batches.append(time_steps(fn, steps, 0, torch, dist) / steps)
+    clocks = smp.stop() if smp else None
     batches.sort()
     ms = batches[1]
     fl = 2.0 * 256 * 8192 * 8192 * 128  # whole job: causal = half of 4*B*H*S^2*D
     world = dist.get_world_size() if dist is not None else 1
     peak = peaks["bf16_tflops"] * world
-    return {"workload": f"FMHA bf16 causal B8 H32 S8192 D128, batch*head sharded x{world}, no collective",
-            "tflops": fl / ms / 1e9, "ms": ms, "ms_batches": batches,
-            "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
-                         "frac": fl / ms / 1e9 / peak}}
+    ent = {"workload": f"FMHA bf16 causal B8 H32 S8192 D128, batch*head sharded x{world}, no collective",
+           "tflops": fl / ms / 1e9, "ms": ms, "ms_batches": batches,
+           "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
+                        "frac": fl / ms / 1e9 / peak, "peak_def": f"bf16 burst x{world}"}}
+    if clocks is not None:
+        with_clocks(ent, clocks)
+    return ent
 
 
+def others_single_gpu(torch, dev, peaks, ops, tf32_peak, flush_buf, gpu_index):
+    """The remaining configurations of the metric, 1 GPU, CUDA-event timed, L2 flushed between
+    launches where the working set fits L2; one second of idle time before each (see settle);
+    every entry carries its own clock sample."""
+    res = []
+    x3_peak = tf32_peak / 3.0
+
+    def timed(entry_fn):
+        settle(torch)
+        smp = ClockSampler(gpu_index).start()
+        ent = entry_fn()
+        return with_clocks(ent, smp.stop())
+
+    # fp32 square sweep
+    for i, n in enumerate((1024, 2048, 4096, 8192)):
+        a, b = uniform(torch, dev, (n, n), 10 + i), uniform(torch, dev, (n, n), 10 + i + 100)
+        c = torch.empty((n, n), device=dev)
+        fn = lambda: ops.matmul_relu(a, b, out=c)
+        for _ in range(3):
+            fn()
+
+        def one():
+            ms = time_flushed(fn, 10, torch, flush_buf)
+            fl = 2.0 * n ** 3
+            return {"workload": f"fp32 matmul+ReLU {n}^3 (3xTF32)", "tflops": fl / ms / 1e9, "ms": ms,
+                    "roofline": {"bound": "tensor", "achieved": fl / ms / 1e9, "peak": x3_peak, "unit": "TFLOP/s",
+                                 "frac": fl / ms / 1e9 / x3_peak}}
+        res.append(timed(one))
+    del a, b, c
+    # FMHA fp32 in/out non-causal B4 H16 S1024 D64
+    g = torch.Generator(device=dev)
+    qkv = []
+    for seed in (20, 21, 22):
+        g.manual_seed(seed)
+        qkv.append(torch.randn((4, 16, 1024, 64), generator=g, device=dev))
+    o = torch.empty_like(qkv[0])
+    fn = lambda: ops.fmha(qkv[0], qkv[1], qkv[2], scale=0.125, out=o)
+    for _ in range(3):
+        fn()
+    fl3 = 4.0 * 4 * 16 * 1024 * 1024 * 64
+
+    def fused():
+        ms = time_flushed(fn, 20, torch, flush_buf)
+        return {"workload": "FMHA fp32-in/out non-causal B4 H16 S1024 D64 (both contractions TF32 on the fp32 tiles, no conversion pass)",
+                "tflops": fl3 / ms / 1e9, "ms": ms, "tolerance": "5e-3 (TF32 internals)",
+                "roofline": {"bound": "tensor", "achieved": fl3 / ms / 1e9, "peak": tf32_peak, "unit": "TFLOP/s",
+                             "frac": fl3 / ms / 1e9 / tf32_peak, "peak_def": "cuBLAS TF32 8192^3 measured live"}}
+    res.append(timed(fused))
+    # the same attention as the reference's un-fused three-operator graph: BatchedMatmul(Q, K^T) ->
+    # Softmax -> BatchedMatmul(P, V) through the standalone kernels (scale folded into Q)
+    qs = qkv[0] * 0.125
+
+    def graph():
+        s = ops.batched_matmul(qs, qkv[1], b_col_major=True, precision="tf32")
+        ops.softmax(s, inplace=True)
+        return ops.batched_matmul(s, qkv[2], precision="tf32")
+    for _ in range(2):
+        graph()
+
+    def unfused():
+        ms = time_steps(graph, 5, 1, torch) / 5
+        return {"workload": "the same attention un-fused: batched matmul (64 x 1024x1024x64, TF32) -> Softmax -> batched matmul "
+                            "(64 x 1024x64x1024), standalone kernels, S materialised (256 MiB)",
+                "tflops": fl3 / ms / 1e9, "ms": ms}
+    res.append(timed(unfused))
+    # standalone Softmax (HBM-bound): 65536 rows x 1024 fp32 in place
+    s = torch.randn((65536, 1024), device=dev) * 3
+    for _ in range(2):
+        ops.softmax(s, inplace=True)
+
+    def soft():
+        ms = time_steps(lambda: ops.softmax(s, inplace=True), 10, 0, torch) / 10
+        nbytes = 2.0 * s.numel() * 4
+        return {"workload": "Softmax 65536 x 1024 fp32 in place (read once, write once)", "gbs": nbytes / ms / 1e6, "ms": ms,
+                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"]}}
+    res.append(timed(soft))
+    del s, qs
+    res.append(fmha_long(torch, dev, peaks, ops, 0, 256, gpu_index))
+    del qkv, o
+    # Transpose (HBM-bound): 8192 x 8192 fp32, 256 MiB in + 256 MiB out, larger than L2
+    x = torch.randn((8192, 8192), device=dev)
+    for _ in range(3):
+        y = ops.transpose(x)
+
+    def tr():
+        ms = time_steps(lambda: ops.transpose(x), 10, 0, torch, None) / 10
+        nbytes = 2.0 * x.numel() * 4
+        return {"workload": "Transpose 8192x8192 fp32 (read once, write once)", "gbs": nbytes / ms / 1e6, "ms": ms,
+                "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"]}}
+    res.append(timed(tr))
+    del x, y
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# small cases for profiler captures:  python bench.py --case <name>
+# ------------------------------------------------------------------------------------------------
+def run_case(args):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from kernelcodegen_b200 import build, ops
+
+    build.build()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+
+    def gemm_bf16(size, copies=0):
+        a = (torch.randn((size, size), device=dev) * 0.02).bfloat16()
+        b = (torch.randn((size, size), device=dev) * 0.02).bfloat16()
+        c = torch.empty((size, size), device=dev, dtype=torch.bfloat16)
+        extra = [torch.empty_like(c) for _ in range(copies)]
+        return (lambda: ops.matmul_relu(a, b, out=c, peers=[t.data_ptr() for t in extra])), 2.0 * size ** 3, "flop"
+
+    def gemm_f32(m, n, k):
+        a, b = uniform(torch, dev, (m, k), 0), uniform(torch, dev, (k, n), 1)
+        c = torch.empty((m, n), device=dev)
+        return (lambda: ops.matmul_relu(a, b, out=c)), 2.0 * m * n * k, "flop"
+
+    def fmha(bq, h, s, d, causal, dtype):
+        q, k, v = (torch.randn((bq, h, s, d), device=dev).to(dtype) for _ in range(3))
+        o = torch.empty_like(q)
+        fl = (2.0 if causal else 4.0) * bq * h * s * s * d
+        return (lambda: ops.fmha(q, k, v, scale=1.0 / math.sqrt(d), causal=causal, out=o)), fl, "flop"
+
+    def transpose():
+        x = torch.randn((8192, 8192), device=dev)
+        return (lambda: ops.transpose(x)), 2.0 * x.numel() * 4, "byte"
+
+    def softmax():
+        x = torch.randn((65536, 1024), device=dev)
+        return (lambda: ops.softmax(x, inplace=True)), 2.0 * x.numel() * 4, "byte"
+
+    def batched():
+        a, b = torch.randn((64, 1024, 64), device=dev), torch.randn((64, 1024, 64), device=dev)
+        return (lambda: ops.batched_matmul(a, b, b_col_major=True, precision="tf32")), 2.0 * 64 * 1024 * 1024 * 64, "flop"
+
+    cases = {
+        "gemm_bf16_8192": lambda: gemm_bf16(8192),
+        "gemm_bf16_16384": lambda: gemm_bf16(16384),
+        "gemm_bf16_8192_7copies": lambda: gemm_bf16(8192, 7),
+        "gemm_3xtf32_c1": lambda: gemm_f32(4096, 2048, 1024),
+        "gemm_3xtf32_1024": lambda: gemm_f32(1024, 1024, 1024),
+        "gemm_3xtf32_8192": lambda: gemm_f32(8192, 8192, 8192),
+        "fmha_causal_b2h16": lambda: fmha(2, 16, 8192, 128, True, torch.bfloat16),
+        "fmha_causal_b1h32": lambda: fmha(1, 32, 8192, 128, True, torch.bfloat16),
+        "fmha_fp32": lambda: fmha(4, 16, 1024, 64, False, torch.float32),
+        "transpose_fp32": transpose,
+        "softmax_fp32": softmax,
+        "batched_qk_tf32": batched,
+    }
+    if args.case not in cases:
+        raise SystemExit(f"unknown case {args.case}; one of {sorted(cases)}")
+    fn, work, unit = cases[args.case]()
+    ms = time_steps(fn, args.iters, 2, torch) / args.iters
+    rate = {"tflops": work / ms / 1e9} if unit == "flop" else {"gbs": work / ms / 1e6}
+    print(json.dumps({"case": args.case, "ms": ms, **rate, "iters": args.iters, "device_status": ops.last_device_status()}),
+          flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
 def run_ours(args):
     # Keep stdout for the one JSON line: anything a library prints to fd 1 (NCCL's version
     # banner, for instance) goes to stderr instead.
     json_fd = os.dup(1)
     os.dup2(2, 1)
+    import numpy as np
     import torch
 
     rank = int(os.environ.get("RANK", "0"))
@@ -439,68 +656,127 @@ def run_ours(args):
     for r0 in range(0, K, chunk):
         b[r0:r0 + chunk] = (torch.randn((chunk, N), generator=g, device=dev) * 0.02).bfloat16()
 
-    cmat = peer.PeerMatrix(M, N, torch.bfloat16, dev) if world > 1 else None
-    c_full = cmat.tensor if cmat is not None else torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    c_local = c_full[lo:hi]
-    peers = cmat.peer_row_ptrs(lo) if cmat is not None else []
-    sync_token = torch.zeros(1, device=dev)
+    # Every rank holds TWO full copies of C (steps alternate between them), so that the flags of
+    # step i can be checked while step i+1 already runs (completion "deferred"); "strict" waits for
+    # all ranks' flags inside every step.
+    completion = args.completion if world > 1 else None
+    n_buf = 2 if completion == "deferred" else 1
+    cmats = [peer.PeerMatrix(M, N, torch.bfloat16, dev, backend=args.peer_backend) for _ in range(n_buf)] if world > 1 else []
+    if world > 1:
+        c_fulls = [cm.tensor for cm in cmats]
+        multicast = bool(cmats[0].mc_ptr) and not args.no_multicast
+        store = ("one multimem.st per 16 bytes through the NVSwitch multicast mapping of C" if multicast
+                 else f"unicast peer stores to {world - 1} peers")
+    else:
+        c_fulls = [torch.empty((M, N), dtype=torch.bfloat16, device=dev)]
+        multicast, store = False, None
+    counter = {"i": 0}
 
     def step():
-        ops.matmul_relu(a, b, out=c_local, peers=peers)
-        if dist is not None:
-            # all ranks' kernels (and with them their stores into this rank's C) are complete
-            # once this stream-ordered all-reduce has run on every rank
-            dist.all_reduce(sync_token)
+        i = counter["i"]
+        counter["i"] = i + 1
+        if world == 1:
+            ops.matmul_relu(a, b, out=c_fulls[0])
+            return
+        cm = cmats[i % n_buf]
+        ops.matmul_relu(a, b, out=cm.tensor[lo:hi], **cm.store_args(lo, i // n_buf + 1, multicast=multicast))
+        if completion == "strict":
+            cm.wait(i // n_buf + 1)         # all ranks' row blocks of step i are in this copy
+        elif i >= 1:
+            prev = cmats[(i - 1) % n_buf]
+            prev.wait((i - 1) // n_buf + 1)  # step i-1 is complete everywhere while step i runs
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    def drain():
+        i = counter["i"]
+        if world > 1 and completion == "deferred" and i >= 1:
+            cmats[(i - 1) % n_buf].wait((i - 1) // n_buf + 1)
+
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
     launches0 = lib.kcg_launch_count()
-    if sampler:
-        sampler.start()
-    ms_total = time_steps(step, args.steps, args.warmup, torch, dist)
+    steps_before = counter["i"]
+    ms_total = time_steps(step, args.steps, args.warmup, torch, dist, drain=drain, preheat_s=args.preheat_s)
     clocks = sampler.stop() if sampler else None
-    launches = lib.kcg_launch_count() - launches0 - 0
+    steps_run = counter["i"] - steps_before
+    launches = lib.kcg_launch_count() - launches0
     # launches counted over warm-up + timed steps on this rank; keep the timed share
-    launches_timed = launches * args.steps // max(1, args.steps + args.warmup)
+    launches_timed = launches * args.steps // max(1, steps_run)
     if dist is not None:
         t = torch.tensor([launches_timed], device=dev, dtype=torch.int64)
         dist.all_reduce(t)
         launches_timed = int(t.item())
-    status = ops.last_device_status()
+    wait_status = capi.status_str(lib.kcg_peer_wait_status())
+    status = 0 if wait_status == "KCG_OK" else wait_status
     ms_step = ms_total / args.steps
     flops = 2.0 * M * N * K
     value = flops / ms_step / 1e9
 
-    # all-gather check (outside the timed region): the first 128 rows of the next rank's block, as
-    # they arrived in THIS rank's copy of C, against a local recomputation from the same seed
+    # all-gather check (outside the timed region): sampled rows of the NEXT rank's block, as they
+    # arrived in THIS rank's copy of C, against the CPU nest in float64 on the same input bits
+    # (first 2048 columns), and the whole arrived block against this rank's own recomputation
     allgather_check = None
     if dist is not None:
+        from oracle import oracle
+
         nxt = (rank + 1) % world
         plo, phi = sharding.row_block(M, nxt, world)
         g2 = torch.Generator(device=dev)
         g2.manual_seed(40 * 100003 + plo)
-        a_peer = (torch.randn((min(chunk, phi - plo), K), generator=g2, device=dev) * 0.02).bfloat16()[:128]
-        want = ops.matmul_relu(a_peer.contiguous(), b)
-        diff = (c_full[plo:plo + 128].float() - want.float()).abs().max()
-        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
-        allgather_check = {"rows_checked_per_rank": 128, "max_abs_diff": float(diff.item())}
-        del a_peer, want
+        a_peer = (torch.randn((min(chunk, phi - plo), K), generator=g2, device=dev) * 0.02).bfloat16()
+        last = cmats[(counter["i"] - 1) % n_buf].tensor
+        pick = [0, 1, 127, 128, 1000, min(chunk, phi - plo) - 1]
+        want64 = oracle.matmul_rows(a_peer[pick].float().cpu().numpy(), b[:, :2048].float().cpu().numpy(),
+                                    list(range(len(pick))), f64=True)
+        want64 = np.maximum(want64, 0.0)
+        got = last[plo:phi][pick][:, :2048].float().cpu().numpy()
+        err = float(np.abs(got - want64).max() / np.abs(want64).max())
+        mine = ops.matmul_relu(a_peer[:256].contiguous(), b, cta_group=1)   # same kernel, same order of sums per tile
+        same = bool(torch.equal(last[plo:plo + 256], mine))
+        t = torch.tensor([err, 0.0 if same else 1.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        allgather_check = {"rows_vs_cpu_nest_f64_per_rank": len(pick), "cols": 2048, "max_rel_err": float(t[0].item()),
+                           "bar": 2e-2, "peer_block_equals_local_recomputation_256_rows": bool(t[1].item() == 0.0)}
+        del a_peer, mine
 
-    # kernel-only duration (no barrier): CUDA events around the GEMM launch alone
-    def gemm_only():
-        ops.matmul_relu(a, b, out=c_local, peers=peers)
-    if dist is not None:
-        dist.barrier()
-    kernel_ms = time_steps(gemm_only, max(3, args.steps // 2), 1, torch, dist) / max(3, args.steps // 2)
-    kernel_tflops = 2.0 * rows * N * K / kernel_ms / 1e9  # this rank's share (max-over-ranks time)
     peak_sust = peaks["bf16_tflops_sustained"]
-    traffic = None
-    if GEMM_BF16_DRAM_BYTES_PER_LAUNCH_8192 is not None:
-        traffic = GEMM_BF16_DRAM_BYTES_PER_LAUNCH_8192 * (rows / 8192.0) * (N / 8192.0) * (K / 8192.0)
-    roofline = {"bound": "tensor", "achieved": kernel_tflops, "peak": peak_sust, "unit": "TFLOP/s",
-                "frac": kernel_tflops / peak_sust, "traffic": traffic,
-                "kernel": "gemm_kernel<bf16, 128x256x64, 4 stages> (tcgen05/TMEM)",
-                "peak_def": f"cuBLAS bf16 sustained, {peak_src} (burst {peaks['bf16_tflops']:.0f}: frac {kernel_tflops / peaks['bf16_tflops']:.3f})",
-                "per_gpu": True, "flop_per_launch": 2.0 * rows * N * K, "kernel_ms": kernel_ms}
+    per_gpu = value / world
+    if DRAM_BYTES_GEMM_BF16["bytes"] is not None:
+        src = DRAM_BYTES_GEMM_BF16
+    else:
+        src = DRAM_BYTES_GEMM_BF16_8192
+    sm_, sn_, sk_ = src["shape"]
+    traffic = src["bytes"] * (rows / sm_) * (N / sn_) * (K / sk_)
+    algo_bytes = 2.0 * (rows * K + K * N + rows * N)
+    roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak_sust, "unit": "TFLOP/s",
+                "frac": per_gpu / peak_sust, "traffic": traffic, "algorithmic_bytes": algo_bytes,
+                "traffic_def": f"ncu dram bytes of one {sm_}^3 launch x tiles x k-blocks of this launch",
+                "kernel": "gemm_kernel<bf16, 128x256x64, 4 stages> (tcgen05/TMEM), one launch per step per GPU",
+                "peak_def": f"cuBLAS bf16 sustained, {peak_src} (burst {peaks['bf16_tflops']:.0f}: frac {per_gpu / peaks['bf16_tflops']:.3f})",
+                "per_gpu": True, "flop_per_launch": 2.0 * rows * N * K,
+                "from": "the timed steps (value / n_gpus)"}
+    if clocks and clocks.get("sm_mhz"):
+        roofline["ms_x_mhz"] = ms_step * clocks["sm_mhz"]
+
+    extra = {}
+    if dist is not None and not args.no_others:
+        # for comparison: the launch alone (no completion wait), and the other completion protocol
+        def gemm_only():
+            cm = cmats[0]
+            ops.matmul_relu(a, b, out=cm.tensor[lo:hi], **cm.store_args(lo, 0, multicast=multicast))
+        kn = max(3, args.steps // 2)
+        extra["kernel_ms_no_wait"] = time_steps(gemm_only, kn, 1, torch, dist) / kn
+        # the literal alternative: GEMM into the local block, then an NCCL all-gather of the blocks
+        blk = torch.empty((rows, N), dtype=torch.bfloat16, device=dev)
+        full = cmats[0].tensor
+
+        def nccl_step():
+            ops.matmul_relu(a, b, out=blk)
+            dist.all_gather_into_tensor(full, blk)
+        if M % world == 0:
+            extra["ms_per_step_gemm_then_nccl_allgather"] = time_steps(nccl_step, kn, 1, torch, dist) / kn
+        del blk
+    c_local = c_fulls[0][lo:hi]
+    peers = cmats[0].peer_row_ptrs(lo) if cmats else []
+    sync_token = torch.zeros(1, device=dev)
 
     # end to end through the public API with host buffers: H2D of this rank's A block and of B,
     # launch, D2H of this rank's C block, every step.  With several ranks each one copies only its
@@ -530,6 +806,7 @@ def run_ours(args):
     e2e_ms = time_steps(e2e_step, e2e_steps, 1, torch, dist) / e2e_steps
     e2e = {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
            "h2d_bytes_per_step": (M * K + K * N) * 2, "d2h_bytes_per_step": M * N * 2,
+           "bound": "PCIe / host memory: 6.4 GB cross the host links every step, whatever the kernels do",
            "note": ("pinned host A + B -> device, GEMM, C -> host, every step, through kcg_gemm_host_staged (row chunks of A / "
                     "column chunks of B copied alternately, each GEMM strip launched when its operands have landed, finished "
                     "strips of C copied back meanwhile)") if not share_b else
@@ -553,19 +830,25 @@ def run_ours(args):
     del a_host, b_host, b_full_host, b_blk, c_host
 
     others = []
+    c1 = None
     tf32_peak = None
     # free the big operands before the other configs
-    del a, b, c_local, c_full
-    if cmat is not None:
-        cmat.close()
+    del a, b, c_local, c_fulls
+    for cm in cmats:
+        cm.close()
+    cmats = []
     torch.cuda.empty_cache()
     if args.no_others:
         pass
     elif world == 1:
-        others, tf32_peak = others_single_gpu(torch, dev, peaks, ops)
+        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        settle(torch)
+        tf32_peak = measure_tf32_peak(torch, dev)
+        c1 = c1_block(torch, dev, ops, tf32_peak / 3.0, tf32_peak, flush_buf, local_rank, with_cpu=not args.no_cpu_baseline)
+        others = others_single_gpu(torch, dev, peaks, ops, tf32_peak, flush_buf, local_rank)
     else:
         blo, bhi = sharding.bh_shard(256, rank, world)
-        others = [fmha_long(torch, dev, peaks, ops, blo, bhi, dist)]
+        others = [fmha_long(torch, dev, peaks, ops, blo, bhi, local_rank if rank == 0 else None, dist)]
     status2 = ops.last_device_status()
 
     cpu = None
@@ -579,10 +862,21 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(world, completion=(
+                None if completion is None else
+                "per-rank flags (st.release.sys by the launch's last CTA) + bounded device-side wait; "
+                + ("checked inside every step" if completion == "strict" else
+                   "the flags of step i are checked while step i+1 runs (two copies of C alternate), all outstanding flags inside the timed region")),
+                store=store, preheat_s=args.preheat_s),
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches_timed, "clocks": clocks,
             "device_status": [status, status2], "others": others,
+            "parity": "partial: the CPU nest the kernels are held to is pinned only by this repository's own float64 fixtures "
+                      "(the reference holds no vectors and cannot be built here)",
         }
+        line.update(extra)
+        if c1 is not None:
+            line["c1"] = c1
         if allgather_check is not None:
             line["allgather_check"] = allgather_check
         if tf32_peak is not None:
@@ -598,13 +892,25 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline legs (N=1)")
     ap.add_argument("--no-others", action="store_true", help="only the headline workload (for profiler launch lists)")
     ap.add_argument("--e2e-chunks", type=int, default=0, help="chunks per operand of the host-buffer GEMM (0 = library default)")
+    ap.add_argument("--completion", choices=("deferred", "strict"), default="deferred",
+                    help="N>1: when the other ranks' completion flags of a step are waited for")
+    ap.add_argument("--peer-backend", choices=("auto", "ipc", "symmetric"), default="auto",
+                    help="N>1: how the ranks' copies of C are made reachable (symmetric memory offers multicast)")
+    ap.add_argument("--no-multicast", action="store_true", help="N>1: unicast peer stores even when a multicast mapping exists")
+    ap.add_argument("--preheat-s", type=float, default=2.0,
+                    help="untimed warm-up continues until this many seconds of steps have run (0 = exactly --warmup steps)")
+    ap.add_argument("--case", default=None, help="run one small case (for profiler captures) and print its timing")
+    ap.add_argument("--iters", type=int, default=3, help="launches of --case")
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = max(args.warmup, 1)
     if args.impl == "reference":

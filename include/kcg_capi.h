@@ -34,8 +34,8 @@ typedef enum kcg_status_t {
   KCG_UNSUPPORTED = 3,    /* dtype / precision / tile combination with no kernel            */
   KCG_CUDA_ERROR = 4,     /* a CUDA runtime/driver call failed                              */
   KCG_DEVICE_TIMEOUT = 5, /* a bounded device-side wait ran out (see kcg_last_device_status)*/
-  KCG_PEER_TIMEOUT = 6,   /* host-side check-in of the ranks timed out                      */
-  KCG_NCCL_ERROR = 7,
+  KCG_PEER_TIMEOUT = 6,   /* a rank did not arrive: host-side check-in, or kcg_peer_wait_launch */
+  /* 7 is not used: the library itself makes no NCCL call */
   KCG_BAD_WORKSPACE = 8,  /* workspace NULL or smaller than kcg_*_workspace_bytes()         */
   KCG_BAD_ARGUMENT = 9,   /* NULL descriptor / NULL tensor pointer                          */
   KCG_TOO_LARGE = 10      /* problem needs more scratch than kcg_gemm_launch_static holds   */
@@ -90,6 +90,21 @@ typedef struct kcg_gemm_desc {
    * below ~4 TFLOP of work, single CTAs for long, power-limited ones). */
   int32_t cta_group;
   void* peer_c[8];
+  /* Fused all-gather through an NVSwitch multicast mapping (optional; NULL = off): the multicast
+   * address of C at this rank's first row.  Every finished 128-byte row segment is then stored
+   * ONCE (multimem.st) and the switch delivers it to all ranks bound to the mapping, this one
+   * included; neither C nor peer_c is written for those segments.  The local C pointer must be
+   * this rank's unicast view of the same memory.  Needs N * sizeof(element of C) % 128 == 0.
+   * The mapping comes from the caller (CUDA multicast objects, e.g. torch symmetric memory). */
+  void* mc_c;
+  /* Completion flags (optional; 0 = none): when the last CTA of the launch has finished, and
+   * after all of the launch's stores of C, done_value is stored (release, system scope) to each
+   * of the n_done_flags 32-bit words -- normally this rank's slot in every rank's flag array
+   * (peer-mapped addresses) -- so that a consumer on any rank can wait for this rank's row
+   * block with kcg_peer_wait_launch instead of a collective. */
+  int32_t n_done_flags;
+  uint32_t done_value;
+  void* done_flags[9];
 } kcg_gemm_desc;
 
 /* O[B,H,Sq,D] = softmax(scale * Q.K^T [+ causal mask]) . V, tensors [B,H,S,D] contiguous
@@ -132,6 +147,15 @@ int kcg_gemm_shared_k_tiles(const kcg_gemm_desc* d);
  * of the tail tiles laid end to end, `span` positions per tile. */
 void kcg_gemm_shared_k_plan(int32_t tiles, int32_t num_kb, int32_t pairs, int32_t tile_n, int32_t* out5);
 
+/* The launch geometry the library will use for a descriptor on a B200 (148 SMs): takes the place
+ * of the `// grid dims:(..), block dims:(..)` comment the reference prints above each kernel
+ * (src/Backend/CUDA.cc:786-791), and is what the generated launcher text quotes.
+ * GEMM  out6 = {CTAs in the grid, threads per CTA, cluster size (2 = CTA pairs), rows and columns
+ *               of one output tile, number of output tiles};
+ * FMHA  out4 = {CTAs in the grid, threads per CTA, queries per CTA, keys per block}. */
+kcg_status_t kcg_gemm_launch_geometry(const kcg_gemm_desc* d, int32_t* out6);
+kcg_status_t kcg_fmha_launch_geometry(const kcg_fmha_desc* d, int32_t* out4);
+
 /* Replaces: launch of `<graph>::kernel0(A, B, C)` emitted by CUDAGen
  * (src/Backend/CUDA.cc:773-857) for the scheduled Matmul func, with Relu fused. */
 kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
@@ -152,7 +176,10 @@ kcg_status_t kcg_gemm_launch(const kcg_gemm_desc* d, const void* A, const void* 
  *   - Only precision KCG_PREC_3XTF32 (the one path that needs scratch); others:
  *     KCG_UNSUPPORTED -- use kcg_gemm_launch with a NULL workspace for those.
  *   - The first call on each device looks up the array's device address; make that first
- *     call before starting any stream capture on that device.
+ *     call before starting any stream capture on that device.  With lazy module loading it is
+ *     also this first call (or any earlier GEMM launch of this library on the device) that
+ *     loads the module and with it reserves the 32 MiB: in a host that reserves the rest of
+ *     the GPU's memory for itself, make it before the host does so, or it can fail.
  *   - All calls on a device share the one array.  Nothing in it has to be cleared between
  *     calls (each call rewrites every byte it later reads), but two calls whose kernels
  *     overlap on the GPU (different streams, no ordering between them) race on it: keep
@@ -232,6 +259,20 @@ kcg_status_t kcg_peer_alloc(size_t bytes, void** out_ptr, void* out_handle64);
 kcg_status_t kcg_peer_open(const void* handle64, void** out_ptr);
 kcg_status_t kcg_peer_close(void* ptr);
 kcg_status_t kcg_peer_free(void* ptr);
+
+/* Waits, on the device and in stream order, until each of the `n` 32-bit flag words
+ * flags[i * stride_words] (i = 0..n-1, device memory of the current GPU that other ranks'
+ * kernels store into, see kcg_gemm_desc.done_flags) has reached `value` (wrap-safe signed
+ * comparison).  One small kernel, one thread per flag, acquire loads at system scope.  The wait
+ * is bounded: after `max_polls` polls per flag (0 = about a second's worth) the kernel gives up,
+ * records code 9 in the device status word and returns, so the stream continues and the context
+ * stays usable; kcg_peer_wait_status then reports KCG_PEER_TIMEOUT.  No counterpart in the
+ * reference, which has no multi-GPU path. */
+kcg_status_t kcg_peer_wait_launch(const void* flags, int32_t n, int32_t stride_words, uint32_t value,
+                                  uint32_t max_polls, void* stream);
+/* Synchronises the device, reads and clears the status word: KCG_OK, KCG_PEER_TIMEOUT when a
+ * kcg_peer_wait_launch gave up, KCG_DEVICE_TIMEOUT for any other bounded wait that ran out. */
+kcg_status_t kcg_peer_wait_status(void);
 
 /* Reads (and clears) the status word of the current device that a kernel sets when one of
  * its bounded waits runs out; 0 = no timeout.  Synchronises the device. */

@@ -19,7 +19,6 @@ KCG_UNSUPPORTED = 3
 KCG_CUDA_ERROR = 4
 KCG_DEVICE_TIMEOUT = 5
 KCG_PEER_TIMEOUT = 6
-KCG_NCCL_ERROR = 7
 KCG_BAD_WORKSPACE = 8
 KCG_BAD_ARGUMENT = 9
 KCG_TOO_LARGE = 10
@@ -36,6 +35,8 @@ EXPORTED_SYMBOLS = (
     "kcg_fmha_workspace_bytes",
     "kcg_gemm_shared_k_tiles",
     "kcg_gemm_shared_k_plan",
+    "kcg_gemm_launch_geometry",
+    "kcg_fmha_launch_geometry",
     "kcg_gemm_launch",
     "kcg_gemm_launch_static",
     "kcg_fmha_fwd_launch",
@@ -51,6 +52,8 @@ EXPORTED_SYMBOLS = (
     "kcg_peer_open",
     "kcg_peer_close",
     "kcg_peer_free",
+    "kcg_peer_wait_launch",
+    "kcg_peer_wait_status",
     "kcg_last_device_status",
     "kcg_set_spin_limit",
     "kcg_selftest_wait_timeout",
@@ -71,6 +74,9 @@ class GemmDesc(Structure):
         ("tile_n", c_int32), ("stages", c_int32), ("group_m", c_int32),
         ("n_peers", c_int32), ("cta_group", c_int32),
         ("peer_c", c_void_p * 8),
+        ("mc_c", c_void_p),
+        ("n_done_flags", c_int32), ("done_value", c_uint32),
+        ("done_flags", c_void_p * 9),
     ]
 
 
@@ -111,6 +117,10 @@ def load() -> ctypes.CDLL:
     lib.kcg_gemm_shared_k_plan.restype = None
     lib.kcg_gemm_shared_k_plan.argtypes = [c_int32, c_int32, c_int32, c_int32, POINTER(c_int32)]
     lib.kcg_fmha_workspace_bytes.argtypes = [POINTER(FmhaDesc)]
+    lib.kcg_gemm_launch_geometry.restype = c_int
+    lib.kcg_gemm_launch_geometry.argtypes = [POINTER(GemmDesc), POINTER(c_int32)]
+    lib.kcg_fmha_launch_geometry.restype = c_int
+    lib.kcg_fmha_launch_geometry.argtypes = [POINTER(FmhaDesc), POINTER(c_int32)]
     lib.kcg_gemm_launch.restype = c_int
     lib.kcg_gemm_launch.argtypes = [POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]
     lib.kcg_gemm_launch_static.restype = c_int
@@ -143,6 +153,10 @@ def load() -> ctypes.CDLL:
     lib.kcg_peer_close.argtypes = [c_void_p]
     lib.kcg_peer_free.restype = c_int
     lib.kcg_peer_free.argtypes = [c_void_p]
+    lib.kcg_peer_wait_launch.restype = c_int
+    lib.kcg_peer_wait_launch.argtypes = [c_void_p, c_int32, c_int32, c_uint32, c_uint32, c_void_p]
+    lib.kcg_peer_wait_status.restype = c_int
+    lib.kcg_peer_wait_status.argtypes = []
     lib.kcg_last_device_status.restype = c_int
     lib.kcg_last_device_status.argtypes = []
     lib.kcg_selftest_wait_timeout.restype = c_int

@@ -125,6 +125,8 @@ extern "C" {
 size_t kcg_gemm_workspace_bytes(const kcg_gemm_desc* d) { return gemm_workspace_impl(d); }
 size_t kcg_fmha_workspace_bytes(const kcg_fmha_desc* d) { return fmha_workspace_impl(d); }
 int kcg_gemm_shared_k_tiles(const kcg_gemm_desc* d) { return gemm_shared_k_tiles_impl(d); }
+kcg_status_t kcg_gemm_launch_geometry(const kcg_gemm_desc* d, int32_t* out6) { return gemm_launch_geometry_impl(d, out6); }
+kcg_status_t kcg_fmha_launch_geometry(const kcg_fmha_desc* d, int32_t* out4) { return fmha_launch_geometry_impl(d, out4); }
 void kcg_gemm_shared_k_plan(int32_t tiles, int32_t num_kb, int32_t pairs, int32_t tile_n, int32_t* out5) {
   if (out5 && tiles > 0 && num_kb > 0 && pairs > 0) gemm_shared_k_plan_impl(tiles, num_kb, pairs, tile_n, out5);
 }
@@ -284,6 +286,43 @@ kcg_status_t kcg_peer_free(void* ptr) {
   return KCG_OK;
 }
 
+// ---- completion flags --------------------------------------------------------------------------
+// One thread per flag polls with acquire loads at system scope until the flag has reached
+// `value`; bounded, see kcg_peer_wait_launch.
+__global__ void peer_wait_kernel(const uint32_t* flags, int n, int stride_words, uint32_t value, uint32_t max_polls,
+                                 int* status) {
+  const int i = threadIdx.x;
+  if (i >= n) return;
+  const uint32_t* f = flags + static_cast<size_t>(i) * stride_words;
+  for (uint32_t it = 0; it < max_polls; ++it) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(f) - value) >= 0) return;
+    __nanosleep(200);
+  }
+  atomicCAS(status, 0, static_cast<int>(DEV_TIMEOUT_PEER));
+}
+
+kcg_status_t kcg_peer_wait_launch(const void* flags, int32_t n, int32_t stride_words, uint32_t value,
+                                  uint32_t max_polls, void* stream) {
+  if (!flags || n <= 0 || n > 32 || stride_words <= 0) return KCG_BAD_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(flags) & 3u) return KCG_BAD_ALIGN;
+  int* status = nullptr;
+  kcg_status_t st = device_status_ptr(&status);
+  if (st != KCG_OK) return st;
+  const uint32_t polls = max_polls ? max_polls : (1u << 22);   // x (200 ns sleep + a load) ~ 1-2 s
+  peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(flags), n,
+                                                                    stride_words, value, polls, status);
+  g_launches.fetch_add(1);
+  KCG_CUDA_TRY(cudaGetLastError());
+  return KCG_OK;
+}
+
+kcg_status_t kcg_peer_wait_status(void) {
+  const int v = kcg_last_device_status();
+  if (v < 0) return KCG_CUDA_ERROR;
+  if (v == 0) return KCG_OK;
+  return v == static_cast<int>(DEV_TIMEOUT_PEER) ? KCG_PEER_TIMEOUT : KCG_DEVICE_TIMEOUT;
+}
+
 // ---- timing helpers (the cost function of the operator API's configuration search) -------------
 static kcg_status_t time_launches(const std::function<kcg_status_t()>& launch, int iters, float* ms) {
   cudaEvent_t e0, e1;
@@ -372,7 +411,6 @@ const char* kcg_status_str(kcg_status_t s) {
     case KCG_CUDA_ERROR: return "KCG_CUDA_ERROR";
     case KCG_DEVICE_TIMEOUT: return "KCG_DEVICE_TIMEOUT";
     case KCG_PEER_TIMEOUT: return "KCG_PEER_TIMEOUT";
-    case KCG_NCCL_ERROR: return "KCG_NCCL_ERROR";
     case KCG_BAD_WORKSPACE: return "KCG_BAD_WORKSPACE";
     case KCG_BAD_ARGUMENT: return "KCG_BAD_ARGUMENT";
     case KCG_TOO_LARGE: return "KCG_TOO_LARGE";

@@ -41,9 +41,6 @@ namespace kcg {
 
 namespace {
 
-#ifndef KCG_FMHA_POLY_PER_8
-#define KCG_FMHA_POLY_PER_8 0
-#endif
 constexpr int FM_THREADS = 384;
 constexpr int BQ = 128;        // query rows per tile
 constexpr int QTILES = 2;      // tiles per CTA
@@ -58,6 +55,10 @@ struct FmhaParams {
   int* status;
   uint32_t spin;
   int after_cast;    // the inputs come from the cast launch just before (programmatic dependent launch)
+  int n_qp;          // 256-query tile pairs per (batch, head)
+  int bh_total;      // batch * heads
+  int bh_group;      // (batch, head) pairs walked together, see the block-index mapping in the kernel
+  int bh_small;      // how many of the groups (the first ones) hold one pair fewer
 };
 
 template <int D, bool TF>
@@ -122,9 +123,26 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int bh = blockIdx.y;
-  // heavy (late) query tiles first when causal
-  const int qpair = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  // Block index -> (batch*head, query tile pair).  CTAs are handed to the SMs in index order as
+  // earlier ones retire, so the order of the indices is the schedule.  Causal tile pairs differ
+  // 32-fold in length at S = 8192: the (batch, head) pairs are walked in groups of `bh_group`, and
+  // within a group the tile pairs of all its heads go longest first, so the launch ends on the
+  // short ones (heads one after the other leave the long tile pairs of the last head to start
+  // when most SMs are already idle: 86 % of the SM-time used at 32 heads, 98 % in groups of 8).
+  // A group's K and V (bh_group heads) stay in L2 while its tile pairs run.
+  // groups are of equal size up to one head: the first `bh_small` groups hold bh_group - 1 heads
+  int idx = blockIdx.x, gsz = p.bh_group - 1, g0 = 0;
+  const int small_items = p.bh_small * gsz * p.n_qp;
+  if (idx >= small_items) {
+    idx -= small_items;
+    gsz = p.bh_group;
+    g0 = p.bh_small * (p.bh_group - 1);
+  }
+  const int grp = idx / (gsz * p.n_qp);
+  g0 += grp * gsz;
+  const int rem = idx - grp * gsz * p.n_qp;
+  const int bh = g0 + rem % gsz;
+  const int qpair = p.causal ? (p.n_qp - 1 - rem / gsz) : (rem / gsz);
   const int q0 = qpair * (QTILES * BQ);
   const int shift = p.Skv - p.Sq;  // causal: query i sees keys j <= i + shift
   // number of key blocks tile t needs (0 when the tile starts beyond Sq)
@@ -345,7 +363,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // until then P may exceed 1 by at most that factor, harmless in bf16/fp32, and O and l stay
     // consistent because both are scaled against the same m.
     constexpr float RESCALE_LOG2 = 8.f;
-    constexpr int POLY_PER_8 = KCG_FMHA_POLY_PER_8;   // pairs out of every 8 whose exp2 runs on the FMA pipe
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_n_kv && ok; ++j) {
@@ -401,10 +418,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // P = exp2(c*s - c*m) as bf16, written over the first 64 columns of this S buffer
       const float mc = (m == -INFINITY) ? 0.f : m * c;
-      // The MUFU unit (16 exp2 per clock per SM) needs as long for a 128x128 block as the
-      // tensor core needs for its two contractions, so a share of the exponentials
-      // (POLY_PER_8 of every 8 pairs) is evaluated on the FMA pipe instead: Cody-Waite range
-      // reduction + cubic minimax polynomial, relative error ~1e-4 (P is rounded to bf16 anyway).
+      // (The MUFU unit, 16 exp2 per clock per SM, needs as long for a 128x128 block as the tensor
+      // core needs for its two contractions; moving a share of the exponentials to an FMA-pipe
+      // polynomial was measured and did not help at this operating point.)
       float2 rsg[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) rsg[g] = make_float2(0.f, 0.f);
@@ -434,12 +450,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; i += 2) {
               float2 x = fma2(make_float2(__uint_as_float(sr[2 * hh + g][i]), __uint_as_float(sr[2 * hh + g][i + 1])),
                               make_float2(c, c), make_float2(-mc, -mc));
-              if (((i >> 1) & 7) < POLY_PER_8) {
-                x = exp2_poly2(x);
-              } else {
-                x.x = ex2_approx(x.x);
-                x.y = ex2_approx(x.y);
-              }
+              x.x = ex2_approx(x.x);
+              x.y = ex2_approx(x.y);
               rsg[(i >> 1) & 3] = add2(rsg[(i >> 1) & 3], x);
               pk[16 * g + (i >> 1)] = pack_bf16x2(x.x, x.y);
             }
@@ -559,7 +571,30 @@ kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   auto kern = fmha_fwd_kernel<D, TF>;
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::SMEM_TOTAL));
-  dim3 grid((p.Sq + QTILES * BQ - 1) / (QTILES * BQ), bh);
+  FmhaParams pp = p;
+  pp.after_cast = after_cast ? 1 : 0;
+  pp.n_qp = (p.Sq + QTILES * BQ - 1) / (QTILES * BQ);
+  pp.bh_total = bh;
+  // heads per group: enough tile pairs for two waves of the SMs, at least 8 heads, and K + V of
+  // a group within a third of the L2 (head dimension D, Skv keys, 2 or 4 bytes per element)
+  {
+    const long long kv_bytes = 2ll * p.Skv * D * (TF ? 4 : 2);
+    const long long l2_heads = (40ll << 20) / (kv_bytes > 0 ? kv_bytes : 1);
+    long long g = (2ll * device_sm_count() + pp.n_qp - 1) / pp.n_qp;
+    if (g < 8) g = 8;
+    if (g > l2_heads) g = l2_heads;
+    if (g < 1) g = 1;
+    if (g > bh) g = bh;
+    // equal groups: a short last group would start its longest tile pairs when the launch is
+    // nearly over
+    const long long n_groups = (bh + g - 1) / g;
+    g = (bh + n_groups - 1) / n_groups;
+    pp.bh_group = static_cast<int>(g);
+    pp.bh_small = static_cast<int>(g * n_groups - bh);
+  }
+  const long long items = static_cast<long long>(pp.n_qp) * bh;
+  if (items > 0x7FFFFFFFll) return KCG_BAD_SHAPE;
+  dim3 grid(static_cast<unsigned>(items));
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -570,14 +605,25 @@ kcg_status_t launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = after_cast ? 1 : 0;
-  FmhaParams pp = p;
-  pp.after_cast = after_cast ? 1 : 0;
   KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, pp));
   g_launches.fetch_add(1);
   return KCG_OK;
 }
 
 }  // namespace
+
+// out = {grid, threads per CTA, queries per CTA, keys per block}
+kcg_status_t fmha_launch_geometry_impl(const kcg_fmha_desc* d, int* out) {
+  if (!d || !out) return KCG_BAD_ARGUMENT;
+  if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0) return KCG_BAD_SHAPE;
+  const long long items = static_cast<long long>((d->Sq + QTILES * BQ - 1) / (QTILES * BQ)) * d->B * d->H;
+  if (items > 0x7FFFFFFFll) return KCG_BAD_SHAPE;
+  out[0] = static_cast<int>(items);
+  out[1] = FM_THREADS;
+  out[2] = QTILES * BQ;
+  out[3] = BKV;
+  return KCG_OK;
+}
 
 size_t fmha_workspace_impl(const kcg_fmha_desc* d) {
   if (!d || d->dtype_in != KCG_F32) return 0;
@@ -592,7 +638,7 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
   if (!d || !Q || !K || !V || !O) return KCG_BAD_ARGUMENT;
   if (d->B <= 0 || d->H <= 0 || d->Sq <= 0 || d->Skv <= 0) return KCG_BAD_SHAPE;
   if (d->D != 64 && d->D != 128) return KCG_BAD_SHAPE;
-  if (static_cast<long long>(d->B) * d->H > 65535) return KCG_BAD_SHAPE;
+  if (static_cast<long long>(d->B) * d->H > 0x7FFFFFll) return KCG_BAD_SHAPE;
   if (d->dtype_in != KCG_F32 && d->dtype_in != KCG_BF16) return KCG_UNSUPPORTED;
   if (d->dtype_out != KCG_F32 && d->dtype_out != KCG_BF16) return KCG_UNSUPPORTED;
   if (!(d->scale > 0.f)) return KCG_BAD_ARGUMENT;

@@ -52,6 +52,16 @@ struct GemmParams {
   uint32_t spin;
   int n_peers;
   void* peers[8];
+  // Multicast form of the fused all-gather: when set, full 128-byte row segments are stored once
+  // to this address (NVSwitch multicast mapping of C at this rank's rows) instead of to C and
+  // to each peer.
+  void* mc;
+  // Completion flags: the CTA that finishes last stores `flag_value` (release, system scope) to
+  // each of these words, after every CTA's stores of C.  `done_counter` counts finished CTAs.
+  int n_flags;
+  uint32_t flag_value;
+  uint32_t* flags[9];
+  int* done_counter;
   // Shared-K tail (CTA-pair kernel): the last `sk_tiles` tiles do not fill a wave of the
   // persistent grid, so their k-blocks, laid end to end (`sk_span` >= num_kb positions per tile;
   // positions past num_kb are padding that makes a tile a whole number of ranges), are cut into
@@ -235,7 +245,23 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
         if (full) {
           __syncwarp();
           const int rr = lane >> 3, ch = lane & 7;
-          for (int dst = 0; dst <= p.n_peers; ++dst) {
+          if (p.mc != nullptr) {
+            // one store per 16 bytes, replicated by the switch to every rank's C (this one's too)
+            uint8_t* cbase = static_cast<uint8_t*>(p.mc);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rloc = i * 4 + rr;
+              const int grow = row0 + rloc;
+              if (grow < p.M) {
+                const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
+                                                                 ((ch ^ (rloc & 7)) << 4));
+                multimem_st_v4(cbase + (static_cast<long long>(grow) * p.ldc + col) *
+                                           static_cast<long long>(sizeof(OutT)) +
+                                   ch * 16, v);
+              }
+            }
+          }
+          for (int dst = (p.mc != nullptr ? 1 : 0); dst <= p.n_peers; ++dst) {
             uint8_t* cbase = static_cast<uint8_t*>(dst == 0 ? p.C : p.peers[dst - 1]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -270,6 +296,22 @@ __device__ __forceinline__ void write_partial(uint32_t t_row, float* dst, int la
     for (int j = 0; j < 8; ++j)
       __stcg(out + (c * 8 + j) * 32, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+  }
+}
+
+// End of a launch that carries completion flags.  Every thread that stored C has executed a
+// system-scope fence after its last store and the CTA has synchronised; one thread per CTA counts
+// the CTA in, and the CTA that finds all the others counted publishes `flag_value` to every flag
+// word (this rank's own and, through their peer mappings, the other ranks').  A consumer that
+// reads the value with an acquire load therefore sees all of this launch's C.
+__device__ __forceinline__ void signal_completion(const GemmParams& p) {
+  if (p.n_flags <= 0) return;
+  __threadfence_system();
+  const int seen = atom_add_acq_rel_gpu(p.done_counter, 1);
+  if (seen == static_cast<int>(gridDim.x) - 1) {
+    *p.done_counter = 0;   // ready for the next launch that is handed this counter
+    __threadfence_system();
+    for (int i = 0; i < p.n_flags; ++i) st_release_sys_u32(p.flags[i], p.flag_value);
   }
 }
 
@@ -466,6 +508,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           __syncwarp();
         }
       }
+      if (!ok) {
+        // Unwinding: UMMAs already issued still read shared memory and write TMEM.  One more
+        // commit arrives on this stage's `empty` barrier when all of them have finished; wait for
+        // it (bounded) before TMEM is freed.  The barrier has completed as many phases as this
+        // stage was passed, so the new arrival completes the phase of parity `phase`.
+        if (elect_one()) umma_commit(bar_empty + 8 * stage);
+        __syncwarp();
+        for (uint32_t it = 0; it < 65536u; ++it)
+          if (mbar_try_wait(bar_empty + 8 * stage, phase)) break;
+      }
     }
   } else {
     // ------------------------------- epilogue (2 groups of 4 warps) --------------------------
@@ -490,10 +542,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
     }
+    if (p.n_flags > 0) __threadfence_system();   // this thread's stores of C, before the flags
   }
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag == 0) signal_completion(p);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
@@ -644,6 +698,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      if (!ok || *abort_flag) {
+        // Unwinding after a wait ran out somewhere in the pair: copies already requested must land
+        // before either CTA's shared memory goes away.  The leader's `full` barriers collect the
+        // bytes of BOTH CTAs' loads, so the leader polls them (bounded) for every stage that was
+        // armed: stages before `stage` in the current phase, the others in the previous one (a
+        // barrier that was never armed passes a wait on parity 1 at once).  The peer CTA cannot
+        // see those barriers complete from its side; it stays resident until the cluster-wide
+        // synchronisation below, which the leader reaches only after this loop.
+        if (rank == 0) {
+          for (int s = 0; s < STAGES; ++s) {
+            const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+            for (uint32_t it = 0; it < 4096u; ++it)
+              if (mbar_try_wait(bar_full + 8 * s, par)) break;
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------- UMMA issuer (leader CTA only) --------------------------
@@ -711,6 +781,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
         }
       }
+      if (!ok) {
+        // Unwinding: UMMAs already issued still read shared memory and write TMEM of both CTAs.
+        // One more commit arrives on a stage barrier when all of them have finished; wait for it
+        // (bounded) before the pair synchronises and frees TMEM.  `empty` of `stage` last saw the
+        // commit of the k-block issued STAGES blocks ago, so the new arrival completes the phase a
+        // producer waiting for that stage would wait on.
+        if (elect_one()) umma_commit_pair(bar_empty + 8 * stage);
+        __syncwarp();
+        for (uint32_t it = 0; it < 65536u; ++it)
+          if (mbar_try_wait(bar_empty + 8 * stage, phase)) break;
+      }
     }
   } else {
     // ------------------------------- epilogue (4 warps, both CTAs) ---------------------------
@@ -757,10 +838,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + 8 * acc);
     }
+    if (p.n_flags > 0) __threadfence_system();   // this thread's stores of C, before the flags
   }
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag == 0) signal_completion(p);
   cluster_sync_all();    // the peer may still signal barriers in this CTA's shared memory until here
   if (warp == 1) {
     tc_fence_after();
@@ -834,6 +917,31 @@ static kcg_status_t sk_counters_ptr(int** out) {
   if (!cache[dev]) {
     void* q = nullptr;
     KCG_CUDA_TRY(cudaGetSymbolAddress(&q, g_sk_counters));
+    if (!q) return KCG_CUDA_ERROR;
+    cache[dev] = static_cast<int*>(q);
+  }
+  *out = cache[dev];
+  return KCG_OK;
+}
+
+// Counters of finished CTAs for launches that publish completion flags: one per launch, handed
+// out round robin (launches that overlap on a device use different ones unless DONE_ROWS of them
+// are in flight), each on its own 128-byte line, left at zero by the launch that used it.
+constexpr int DONE_ROWS = 32;
+constexpr int DONE_STRIDE = 32;
+static __device__ int g_done_counters[DONE_ROWS * DONE_STRIDE];
+std::atomic<unsigned> g_done_row{0};
+
+static kcg_status_t done_counters_ptr(int** out) {
+  static std::mutex mu;
+  static int* cache[64] = {};
+  int dev = 0;
+  KCG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KCG_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* q = nullptr;
+    KCG_CUDA_TRY(cudaGetSymbolAddress(&q, g_done_counters));
     if (!q) return KCG_CUDA_ERROR;
     cache[dev] = static_cast<int*>(q);
   }
@@ -1034,6 +1142,7 @@ void gemm_shared_k_plan_impl(int tiles, int num_kb, int pairs, int bn, int* out)
 void gemm_reset_shared_k_counters() {
   int* counters = nullptr;
   if (sk_counters_ptr(&counters) == KCG_OK) cudaMemset(counters, 0, sizeof(int) * SK_ROWS * SK_ROW_INTS);
+  if (done_counters_ptr(&counters) == KCG_OK) cudaMemset(counters, 0, sizeof(int) * DONE_ROWS * DONE_STRIDE);
 }
 
 // Tail tiles the shared-K plan covers for this descriptor on 74 CTA pairs (0 = no shared-K tail).
@@ -1048,6 +1157,35 @@ int gemm_shared_k_tiles_impl(const kcg_gemm_desc* d) {
   const long long tiles = ((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn);
   if (tiles > 0x7FFFFFFF) return 0;
   return plan_shared_k(static_cast<int>(tiles), static_cast<int>((d->K + bk - 1) / bk), 74, bn).tiles;
+}
+
+// Launch geometry for a descriptor on a B200 (148 SMs / 74 CTA pairs):
+// out = {grid, threads per CTA, cluster size, tile rows, tile columns, output tiles}.
+kcg_status_t gemm_launch_geometry_impl(const kcg_gemm_desc* d, int* out) {
+  if (!d || !out) return KCG_BAD_ARGUMENT;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0 || d->M > 0x7FFFFFFF || d->N > 0x7FFFFFFF) return KCG_BAD_SHAPE;
+  int bn = 0;
+  bool pair_mode = false;
+  resolve_variant(d, &bn, &pair_mode);
+  if (bn != 128 && bn != 256) return KCG_UNSUPPORTED;
+  const int tile_m = pair_mode ? 2 * BM : BM;
+  const long long tiles = ((d->M + tile_m - 1) / tile_m) * ((d->N + bn - 1) / bn);
+  if (tiles > 0x7FFFFFFF) return KCG_BAD_SHAPE;
+  const int units = pair_mode ? 74 : 148;
+  long long resident = tiles < units ? tiles : units;
+  if (pair_mode && tiles < units) {
+    // fewer tiles than pairs: the shared-K plan may spread them over more pairs
+    const int bk = d->precision == KCG_PREC_BF16 ? 64 : 32;
+    const SkPlan pl = plan_shared_k(static_cast<int>(tiles), static_cast<int>((d->K + bk - 1) / bk), units, bn);
+    if (pl.tiles > 0 && pl.units > resident) resident = pl.units;
+  }
+  out[0] = static_cast<int>(pair_mode ? 2 * resident : resident);
+  out[1] = pair_mode ? GEMM_THREADS : GEMM1_THREADS;
+  out[2] = pair_mode ? 2 : 1;
+  out[3] = tile_m;
+  out[4] = bn;
+  out[5] = static_cast<int>(tiles);
+  return KCG_OK;
 }
 
 // bytes of the 3xTF32 residual arrays at the head of the workspace
@@ -1102,6 +1240,13 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   if ((d->lda * es) % 16 || (d->ldb * es) % 16 || (d->ldc * os) % 16) return KCG_BAD_ALIGN;
   for (int i = 0; i < d->n_peers; ++i)
     if (!d->peer_c[i] || !aligned16(d->peer_c[i])) return KCG_BAD_ALIGN;
+  if (d->mc_c) {
+    // the multicast path stores whole 128-byte row segments only
+    if (!aligned16(d->mc_c) || (d->N * os) % 128) return KCG_BAD_ALIGN;
+  }
+  if (d->n_done_flags < 0 || d->n_done_flags > 9) return KCG_BAD_ARGUMENT;
+  for (int i = 0; i < d->n_done_flags; ++i)
+    if (!d->done_flags[i] || (reinterpret_cast<uintptr_t>(d->done_flags[i]) & 3u)) return KCG_BAD_ALIGN;
   int bn = 0;
   bool pair_mode = false;
   resolve_variant(d, &bn, &pair_mode);
@@ -1191,6 +1336,17 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   p.spin = spin ? spin : KCG_SPIN_LIMIT;
   p.n_peers = d->n_peers;
   for (int i = 0; i < 8; ++i) p.peers[i] = i < d->n_peers ? d->peer_c[i] : nullptr;
+  p.mc = d->mc_c;
+  p.n_flags = d->n_done_flags;
+  p.flag_value = d->done_value;
+  for (int i = 0; i < 9; ++i) p.flags[i] = i < d->n_done_flags ? static_cast<uint32_t*>(d->done_flags[i]) : nullptr;
+  p.done_counter = nullptr;
+  if (p.n_flags > 0) {
+    int* counters = nullptr;
+    st = done_counters_ptr(&counters);
+    if (st != KCG_OK) return st;
+    p.done_counter = counters + (g_done_row.fetch_add(1) % DONE_ROWS) * DONE_STRIDE;
+  }
   p.sk_tiles = p.sk_units = p.sk_share = p.sk_span = p.sk_maxc = 0;
   p.sk_partial = nullptr;
   p.sk_count = nullptr;

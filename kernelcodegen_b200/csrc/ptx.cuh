@@ -21,6 +21,7 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_PV = 6,         // softmax warps waited too long for P.V
   DEV_TIMEOUT_P = 7,          // MMA issuer waited too long for P in shared memory
   DEV_TIMEOUT_Q = 8,          // MMA issuer waited too long for the Q tile
+  DEV_TIMEOUT_PEER = 9,       // a rank's completion flag did not arrive in time (kcg_peer_wait_launch)
 };
 
 #ifndef KCG_SPIN_LIMIT
@@ -110,6 +111,24 @@ __device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
   int old;
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
   return old;
+}
+
+// ---- stores and flags that other GPUs see ------------------------------------------------------
+// One 16-byte store to a multicast address: the NVSwitch delivers it to the same offset of every
+// GPU bound to the multicast object (this GPU included), so a tile leaves the SM once however
+// many ranks receive it.  The payload is opaque bits (the .f32 type only names the width).
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
 }
 
 // ---- TMA loads (each CTA loads its own tiles) ------------------------------------------------
@@ -363,25 +382,6 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   float2 d;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(pd));
   return d;
-}
-
-// 2^x for a pair of values on the FMA/ALU pipes (no MUFU): x is clamped to >= -126, split into
-// n = round(x) and f = x - n in [-0.5, 0.5] with the 1.5*2^23 trick, 2^f by a cubic minimax
-// polynomial (max relative error 7.6e-5 on [-0.5, 0.5]), and n added into the exponent field.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  const float MAGIC = 12582912.f;  // 1.5 * 2^23
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = add2(x, make_float2(MAGIC, MAGIC));
-  const float2 n = add2(t, make_float2(-MAGIC, -MAGIC));
-  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
-  float2 pz = fma2(f, make_float2(0.0552055053f, 0.0552055053f), make_float2(0.2426139712f, 0.2426139712f));
-  pz = fma2(pz, f, make_float2(0.6932547688f, 0.6932547688f));
-  pz = fma2(pz, f, make_float2(0.9999276996f, 0.9999276996f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(pz.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(pz.y) + (__float_as_int(t.y) << 23));
-  return r;
 }
 
 }  // namespace kcg

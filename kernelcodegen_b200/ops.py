@@ -54,11 +54,15 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
 def matmul(a: torch.Tensor, b: torch.Tensor, *, relu: bool = False, precision: Optional[str] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
            b_col_major: bool = False, tile_n: int = 0, stages: int = 0, group_m: int = 0,
-           cta_group: int = 0, peers: Sequence[int] = ()) -> torch.Tensor:
+           cta_group: int = 0, peers: Sequence[int] = (), mc: int = 0, done_flags: Sequence[int] = (),
+           done_value: int = 0) -> torch.Tensor:
     """C = A . B (optionally ReLU'd).  A is [M, K] row-major; B is [K, N] row-major, or
     [N, K] when `b_col_major` (the reference's Layout::colMajor).  fp32 inputs use the
     3xTF32 path unless `precision="tf32"`; bf16 inputs use the bf16 path.
-    `peers` are raw device pointers of other ranks' C buffers that also receive every tile."""
+    `peers` are raw device pointers of other ranks' C buffers that also receive every tile;
+    `mc` is the multicast address of `out` (every tile is then stored once and delivered to all
+    ranks by the switch); `done_flags` are the words that receive `done_value` when the launch,
+    and all its stores, have completed (see `peer.SymmetricMatrix`)."""
     dev = _require_cuda(a, b)
     if a.dim() != 2 or b.dim() != 2:
         raise ValueError("matmul takes 2-D tensors")
@@ -95,6 +99,11 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, relu: bool = False, precision: O
     d.n_peers = len(peers)
     for i, p in enumerate(peers):
         d.peer_c[i] = p
+    d.mc_c = mc or None
+    d.n_done_flags = len(done_flags)
+    d.done_value = done_value & 0xFFFFFFFF
+    for i, p in enumerate(done_flags):
+        d.done_flags[i] = p
     lib = capi.load()
     with torch.cuda.device(dev):
         ws_bytes = lib.kcg_gemm_workspace_bytes(ctypes.byref(d))
@@ -258,6 +267,20 @@ def batched_matmul(a: torch.Tensor, b: torch.Tensor, *, b_col_major: bool = Fals
                                          torch.cuda.current_stream(dev).cuda_stream)
     capi.check(st, "kcg_batched_gemm_launch")
     return out
+
+
+def peer_wait(flags_ptr: int, n: int, stride_words: int, value: int, device: torch.device, max_polls: int = 0) -> None:
+    """Queues, on the current stream, a bounded device-side wait until the `n` flag words at
+    `flags_ptr` (stride in 32-bit words) have reached `value`."""
+    with torch.cuda.device(device):
+        st = capi.load().kcg_peer_wait_launch(flags_ptr, n, stride_words, value & 0xFFFFFFFF, max_polls,
+                                              torch.cuda.current_stream(device).cuda_stream)
+    capi.check(st, "kcg_peer_wait_launch")
+
+
+def peer_wait_status() -> None:
+    """Synchronises and raises KcgError(KCG_PEER_TIMEOUT / KCG_DEVICE_TIMEOUT) if a bounded wait ran out."""
+    capi.check(capi.load().kcg_peer_wait_status(), "kcg_peer_wait_status")
 
 
 def last_device_status() -> int:

@@ -297,9 +297,10 @@ std::string CUDAGen(mlir::ModuleOp& module) {
     if (p.kind == LaunchPlan::Kind::Gemm) {
       const auto& d = p.gemm;
       const char* ct = d.dtype_in == KCG_BF16 ? "void" : "float";
-      const int64_t bn = d.tile_n ? d.tile_n : (d.precision == KCG_PREC_3XTF32 ? 128 : 256);
-      os << "// grid dims:(min(#SM, " << ((d.M + 127) / 128) * ((d.N + bn - 1) / bn) << " tiles), ), block dims:(192, )"
-         << "  tile 128x" << bn << ", persistent\n";
+      int32_t geo[6] = {0, 0, 0, 0, 0, 0};
+      if (kcg_gemm_launch_geometry(&d, geo) == KCG_OK)
+        os << "// grid dims:(" << geo[0] << ", ), block dims:(" << geo[1] << ", )  cluster " << geo[2] << ", tile " << geo[3]
+           << "x" << geo[4] << ", " << geo[5] << " tiles, persistent (on 148 SMs)\n";
       os << "inline kcg_status_t kernel" << kid << "(const " << ct << "* A, const " << ct << "* B, " << ct
          << "* C, void* workspace, size_t workspace_bytes, cudaStream_t stream) {\n"
          << "  kcg_gemm_desc d = {};\n"
@@ -314,7 +315,10 @@ std::string CUDAGen(mlir::ModuleOp& module) {
     } else {
       const auto& d = p.fmha;
       const char* ct = d.dtype_in == KCG_BF16 ? "void" : "float";
-      os << "// grid dims:(" << (d.Sq + 127) / 128 << ", " << d.B * d.H << ", ), block dims:(192, )\n";
+      int32_t geo[4] = {0, 0, 0, 0};
+      if (kcg_fmha_launch_geometry(&d, geo) == KCG_OK)
+        os << "// grid dims:(" << geo[0] << ", ), block dims:(" << geo[1] << ", )  " << geo[2] << " queries per CTA, key blocks of "
+           << geo[3] << "\n";
       os << "inline kcg_status_t kernel" << kid << "(const " << ct << "* Q, const " << ct << "* K, const " << ct
          << "* V, " << ct << "* O, void* workspace, size_t workspace_bytes, cudaStream_t stream) {\n"
          << "  kcg_fmha_desc d = {};\n"

@@ -25,9 +25,27 @@ def test_every_declared_symbol_is_exported(native_lib):
     assert set(capi.EXPORTED_SYMBOLS) <= set(names)
 
 
-def test_struct_sizes_match_header():
-    assert ctypes.sizeof(capi.GemmDesc) == 6 * 8 + 10 * 4 + 8 * 8
-    assert ctypes.sizeof(capi.FmhaDesc) == 10 * 4
+def test_struct_layouts_match_header(tmp_path):
+    """sizeof / offsetof of every descriptor field as a C compiler lays out include/kcg_capi.h,
+    against the ctypes mirrors the Python callers use."""
+    import subprocess
+
+    lines = []
+    for cname, cls in (("kcg_gemm_desc", capi.GemmDesc), ("kcg_fmha_desc", capi.FmhaDesc)):
+        lines.append(f'printf("%zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            lines.append(f'printf("%zu\\n", offsetof({cname}, {fname}));')
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "kcg_capi.h"\nint main(void) {\n'
+                   + "\n".join(lines) + "\nreturn 0; }\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    want = []
+    for cls in (capi.GemmDesc, capi.FmhaDesc):
+        want.append(ctypes.sizeof(cls))
+        want += [getattr(cls, fname).offset for fname, _ in cls._fields_]
+    assert got == want
 
 
 def test_status_strings(native_lib):
@@ -185,3 +203,24 @@ def test_shared_k_plan_covers_every_k_block_once(native_lib):
                     assert contrib[ti] == set(range(first, last + 1))      # what the epilogue counts on
                     assert len(contrib[ti]) <= maxc
     assert planned > 100
+
+
+def test_launch_geometry_follows_the_variant_choice(native_lib):
+    """The geometry the generated launcher text quotes: CTA pairs with 256x128 tiles for the
+    short fp32 launch, single 320-thread CTAs with 128x256 tiles for the long bf16 one; one CTA
+    per 256 queries and (batch, head) for attention."""
+    out = (ctypes.c_int32 * 6)()
+    d = _gemm_desc(4096, 2048, 1024)
+    assert native_lib.kcg_gemm_launch_geometry(ctypes.byref(d), out) == capi.KCG_OK
+    assert list(out) == [148, 192, 2, 256, 128, 256]
+    d = _gemm_desc(32768, 32768, 32768, prec=capi.KCG_PREC_BF16, dt=capi.KCG_BF16)
+    assert native_lib.kcg_gemm_launch_geometry(ctypes.byref(d), out) == capi.KCG_OK
+    assert list(out) == [148, 320, 1, 128, 256, 256 * 128]
+    d = _gemm_desc(128, 128, 128)           # one tile
+    assert native_lib.kcg_gemm_launch_geometry(ctypes.byref(d), out) == capi.KCG_OK
+    assert list(out)[:5] == [1, 320, 1, 128, 128]
+    f = capi.FmhaDesc()
+    f.B, f.H, f.Sq, f.Skv, f.D = 8, 32, 8192, 8192, 128
+    out4 = (ctypes.c_int32 * 4)()
+    assert native_lib.kcg_fmha_launch_geometry(ctypes.byref(f), out4) == capi.KCG_OK
+    assert list(out4) == [32 * 256, 384, 256, 128]

@@ -15,19 +15,28 @@ def rel_err(x, ref):
     return float(np.abs(x - ref).max() / max(np.abs(ref).max(), 1e-30))
 
 
-@pytest.mark.parametrize("shape", [(5, 7, 33), (4, 128), (3, 1000), (2, 3, 1024), (6, 4100), (1, 1), (2, 8192)])
+@pytest.mark.parametrize("shape", [(5, 7, 33), (4, 128), (3, 1000), (2, 3, 1024), (6, 4100), (1, 1), (2, 8192), (300, 516), (3, 2050),
+                                   (2, 16384), (1, 49152), (2, 50000)])
 def test_softmax_matches_oracle(cuda_device, shape):
     from kernelcodegen_b200 import ops
 
     g = torch.Generator().manual_seed(sum(shape))
     x = torch.randn(shape, generator=g) * 3
     want = oracle.softmax(x.numpy())
+    # The nest adds a row's exponentials one after the other in fp32; on rows of tens of thousands
+    # of columns that sum alone drifts past 1e-5 of the exact quotient.  The kernel is held to
+    # 1e-5 of the float64 value, and to the nest within the nest's own distance from it.
+    x64 = x.numpy().astype(np.float64)
+    e = np.exp(x64 - x64.max(-1, keepdims=True))
+    exact = e / e.sum(-1, keepdims=True)
+    nest_drift = rel_err(want, exact)
     got = ops.softmax(x.to(cuda_device))
-    assert rel_err(got.cpu().numpy(), want) <= 1e-5
+    assert rel_err(got.cpu().numpy(), exact) <= 1e-5
+    assert rel_err(got.cpu().numpy(), want) <= 1e-5 + nest_drift
     np.testing.assert_allclose(got.sum(-1).cpu().numpy(), 1.0, atol=1e-5)
     xin = x.to(cuda_device).clone()
     assert ops.softmax(xin, inplace=True) is xin
-    assert rel_err(xin.cpu().numpy(), want) <= 1e-5
+    assert rel_err(xin.cpu().numpy(), exact) <= 1e-5
 
 
 def test_softmax_golden(cuda_device, golden):

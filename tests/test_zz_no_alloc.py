@@ -7,7 +7,9 @@ hit the device-wide synchronisation an allocation brings -- so they cannot pass 
 fixed 32 MiB scratch array per GPU.  This test calls that entry point through the C-ABI twice
 in a row, with different shapes and data, and holds each result to the workspace-taking entry
 point's result (same kernels, so the same 1e-4 bar as the other fp32 tests; in practice they
-agree bit for bit).  It also checks that a problem beyond the built-in scratch is refused.
+agree bit for bit) and to the CPU nest.  It also checks that repeated calls change neither the
+device's free memory nor torch's allocator statistics, and that a problem beyond the built-in
+scratch is refused.
 
 The file name sorts last on purpose: a run that stops at the first failure has by then run
 every other test.
@@ -37,7 +39,10 @@ def _rel_err(x, ref):
 
 
 def test_static_scratch_entry_matches_workspace_entry_twice(cuda_device):
+    import numpy as np
+
     from kernelcodegen_b200 import capi, ops
+    from oracle import oracle
 
     lib = capi.load()
     stream = torch.cuda.current_stream(cuda_device).cuda_stream
@@ -45,8 +50,9 @@ def test_static_scratch_entry_matches_workspace_entry_twice(cuda_device):
     # beyond the second call's extent must not leak into its result
     for call, (m, n, k, seed) in enumerate([(512, 1024, 768, 1), (256, 384, 200, 2)]):
         g = torch.Generator().manual_seed(seed)
-        a = (torch.rand((m, k), generator=g) * 2 - 1).to(cuda_device)
-        b = (torch.rand((k, n), generator=g) * 2 - 1).to(cuda_device)
+        a_h = torch.rand((m, k), generator=g) * 2 - 1
+        b_h = torch.rand((k, n), generator=g) * 2 - 1
+        a, b = a_h.to(cuda_device), b_h.to(cuda_device)
         want = ops.matmul_relu(a, b)  # existing entry point, workspace allocated by the caller
         got = torch.full((m, n), float("nan"), device=cuda_device)
         d = _desc(capi, m, n, k)
@@ -56,6 +62,33 @@ def test_static_scratch_entry_matches_workspace_entry_twice(cuda_device):
         assert ops.last_device_status() == 0
         assert torch.isfinite(got).all()
         assert _rel_err(got, want) <= FP32_TOL, f"call {call}"
+        # and against the CPU nest itself, not only against the library's other entry point
+        cpu = torch.from_numpy(oracle.matmul_relu(a_h.numpy(), b_h.numpy()))
+        assert _rel_err(got.cpu(), cpu) <= FP32_TOL, f"call {call} vs the CPU nest"
+
+
+def test_static_scratch_entry_allocates_nothing(cuda_device):
+    """After a first call (which loads the module holding the scratch array and looks up its
+    address), further calls leave the device's free memory and torch's allocator untouched."""
+    from kernelcodegen_b200 import capi
+
+    lib = capi.load()
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    m, n, k = 384, 512, 256
+    a = torch.rand((m, k), device=cuda_device)
+    b = torch.rand((k, n), device=cuda_device)
+    c = torch.empty((m, n), device=cuda_device)
+    d = _desc(capi, m, n, k)
+    assert lib.kcg_gemm_launch_static(ctypes.byref(d), a.data_ptr(), b.data_ptr(), c.data_ptr(), stream) == capi.KCG_OK
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(cuda_device)
+    stats0 = (torch.cuda.memory_allocated(cuda_device), torch.cuda.memory_reserved(cuda_device))
+    for _ in range(5):
+        assert lib.kcg_gemm_launch_static(ctypes.byref(d), a.data_ptr(), b.data_ptr(), c.data_ptr(), stream) == capi.KCG_OK
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free1 == free0, "device free memory changed across calls that must not allocate"
+    assert (torch.cuda.memory_allocated(cuda_device), torch.cuda.memory_reserved(cuda_device)) == stats0
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit(cuda_device):
