@@ -239,19 +239,12 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # timing helpers
 # ------------------------------------------------------------------------------------------------
-def workload_config(n, completion=None, store=None, preheat_s=None):
-    cfg = {"workload": "large bf16 matmul+ReLU M=N=K=32768 (bf16 in N(0,0.02), fp32 accumulate, bf16 out), "
-                       "A/C sharded by row blocks, C all-gathered by the GEMM epilogue's own stores",
-           "M": LARGE, "N": LARGE, "K": LARGE, "parallelism": f"row-block x{n}",
-           "cache": "inputs (2 GiB per operand) are larger than L2 (126 MB); no flush needed"}
-    if completion:
-        cfg["completion"] = completion
-    if store:
-        cfg["allgather_store"] = store
-    if preheat_s is not None:
-        cfg["preheat"] = (f"untimed warm-up steps continue until {preheat_s:g} s of work have run, so that the timed steps "
-                          "see the steady power-capped clocks at every N")
-    return cfg
+def workload_config(n):
+    """The workload, in the same words for both arms (what a run did beyond that goes into `run`)."""
+    return {"workload": "large bf16 matmul+ReLU M=N=K=32768 (bf16 in N(0,0.02), fp32 accumulate, bf16 out), "
+                        "A/C sharded by row blocks, C all-gathered by the GEMM epilogue's own stores",
+            "M": LARGE, "N": LARGE, "K": LARGE, "parallelism": f"row-block x{n}",
+            "cache": "inputs (2 GiB per operand) are larger than L2 (126 MB); no flush needed"}
 
 
 def time_steps(fn, steps, warmup, torch, dist=None, drain=None, preheat_s=0.0):
@@ -397,6 +390,23 @@ def c1_block(torch, dev, ops, x3_peak, tf32_peak, flush_buf, gpu_index, with_cpu
                              "against": "the full fp32 nest + ReLU on the CPU, same input bits", "pinned": False}
         except Exception as ex:
             blk["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+        # the same nests as the operator API's own Frontend builds them, lowered to scalar LLVM IR and
+        # JIT-compiled for the host: "the repo's own affine module lowered to CPU"
+        try:
+            from oracle import module_jit
+
+            threads = host_threads()
+            mod = module_jit.LoweredModule("matmul_relu", (M, N, K))
+            t0 = time.perf_counter()
+            c_mod = mod.run(a_np, b_np, threads=threads)
+            t = time.perf_counter() - t0
+            blk["cpu_baseline_module"] = {
+                "value": fl / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "module",
+                "sample": f"the Frontend's Matmul + Relu module for {M}x{K}x{N}, lowered to LLVM IR, JIT-compiled, rows over host threads, {t:.1f} s",
+                "equals_port_bitwise": bool(np.array_equal(c_mod, want)),
+                "max_rel_err_of_gpu_result": float(np.abs(got - c_mod).max() / np.abs(c_mod).max())}
+        except Exception as ex:
+            blk["cpu_baseline_module"] = {"value": None, "kind": "module", "sample": f"unavailable: {ex}"}
     return blk
 
 
@@ -641,20 +651,50 @@ def run_ours(args):
     peaks, peak_src = load_peaks()
 
     M = N = K = LARGE
-    lo, hi = sharding.row_block(M, rank, world)
-    rows = hi - lo
-    # inputs: generated per row block from the seed, so each rank only makes its shard of A
-    g = torch.Generator(device=dev)
-    g.manual_seed(40 * 100003 + lo)
-    a = torch.empty((rows, K), dtype=torch.bfloat16, device=dev)
     chunk = 2048
-    for r0 in range(0, rows, chunk):
-        r1 = min(rows, r0 + chunk)
-        a[r0:r1] = (torch.randn((r1 - r0, K), generator=g, device=dev) * 0.02).bfloat16()
+    g = torch.Generator(device=dev)
     g.manual_seed(41)
     b = torch.empty((K, N), dtype=torch.bfloat16, device=dev)
     for r0 in range(0, K, chunk):
         b[r0:r0 + chunk] = (torch.randn((chunk, N), generator=g, device=dev) * 0.02).bfloat16()
+
+    def make_a(r_lo, r_hi):
+        """Rows [r_lo, r_hi) of A: every 128-row block has its own seed, so a rank makes exactly its
+        shard and the bits do not depend on how the rows are dealt out."""
+        out = torch.empty((r_hi - r_lo, K), dtype=torch.bfloat16, device=dev)
+        for r0 in range(r_lo - r_lo % 128, r_hi, 128):
+            g.manual_seed(40 * 100003 + r0)
+            blk = (torch.randn((128, K), generator=g, device=dev) * 0.02).bfloat16()
+            s0, s1 = max(r0, r_lo), min(r0 + 128, r_hi)
+            out[s0 - r_lo:s1 - r_lo] = blk[s0 - r0:s1 - r0]
+        return out
+
+    # Row blocks.  The GPUs of one node run this power-capped GEMM at rates several per cent apart,
+    # and a step ends when the slowest rank ends: each rank first times the product on an equal
+    # block (no stores to peers), and the rows are then dealt out in proportion to the measured
+    # rates, in blocks of 128 rows.
+    blocks = [sharding.row_block(M, r, world) for r in range(world)]
+    rank_rates = None
+    if world > 1 and not args.equal_rows:
+        e_lo, e_hi = blocks[rank]
+        a_eq = make_a(e_lo, e_hi)
+        c_eq = torch.empty((e_hi - e_lo, N), dtype=torch.bfloat16, device=dev)
+        cal = lambda: ops.matmul_relu(a_eq, b, out=c_eq)
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < args.preheat_s:     # to the steady power-capped clocks first
+            for _ in range(4):
+                cal()
+            torch.cuda.synchronize()
+        cal_ms = time_steps(cal, 6, 1, torch) / 6
+        rate = torch.tensor([2.0 * (e_hi - e_lo) * N * K / cal_ms / 1e9], device=dev, dtype=torch.float64)
+        rates = [torch.zeros_like(rate) for _ in range(world)]
+        dist.all_gather(rates, rate)
+        rank_rates = [float(r.item()) for r in rates]
+        blocks = sharding.weighted_row_blocks(M, rank_rates)
+        del a_eq, c_eq
+    lo, hi = blocks[rank]
+    rows = hi - lo
+    a = make_a(lo, hi)
 
     # Every rank holds TWO full copies of C (steps alternate between them), so that the flags of
     # step i can be checked while step i+1 already runs (completion "deferred"); "strict" waits for
@@ -718,18 +758,17 @@ def run_ours(args):
         from oracle import oracle
 
         nxt = (rank + 1) % world
-        plo, phi = sharding.row_block(M, nxt, world)
-        g2 = torch.Generator(device=dev)
-        g2.manual_seed(40 * 100003 + plo)
-        a_peer = (torch.randn((min(chunk, phi - plo), K), generator=g2, device=dev) * 0.02).bfloat16()
+        plo, phi = blocks[nxt]
+        a_peer = torch.cat([make_a(plo, plo + 256), make_a(phi - 128, phi)])     # first 256 rows and the last 128
+        peer_rows = list(range(plo, plo + 256)) + list(range(phi - 128, phi))
         last = cmats[(counter["i"] - 1) % n_buf].tensor
-        pick = [0, 1, 127, 128, 1000, min(chunk, phi - plo) - 1]
+        pick = [0, 1, 127, 128, 255, 256 + 127]                                  # indices into a_peer
         want64 = oracle.matmul_rows(a_peer[pick].float().cpu().numpy(), b[:, :2048].float().cpu().numpy(),
                                     list(range(len(pick))), f64=True)
         want64 = np.maximum(want64, 0.0)
-        got = last[plo:phi][pick][:, :2048].float().cpu().numpy()
+        got = last[[peer_rows[i] for i in pick]][:, :2048].float().cpu().numpy()
         err = float(np.abs(got - want64).max() / np.abs(want64).max())
-        mine = ops.matmul_relu(a_peer[:256].contiguous(), b, cta_group=1)   # same kernel, same order of sums per tile
+        mine = ops.matmul_relu(a_peer[:256].contiguous(), b, cta_group=1, tile_n=256)   # same kernel, same order of sums per tile
         same = bool(torch.equal(last[plo:plo + 256], mine))
         t = torch.tensor([err, 0.0 if same else 1.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -764,6 +803,11 @@ def run_ours(args):
             ops.matmul_relu(a, b, out=cm.tensor[lo:hi], **cm.store_args(lo, 0, multicast=multicast))
         kn = max(3, args.steps // 2)
         extra["kernel_ms_no_wait"] = time_steps(gemm_only, kn, 1, torch, dist) / kn
+        # every rank's own time for its block with the stores (no waiting on anybody), rank order
+        mine_ms = torch.tensor([time_steps(gemm_only, kn, 1, torch) / kn], device=dev, dtype=torch.float64)
+        all_ms = [torch.zeros_like(mine_ms) for _ in range(world)]
+        dist.all_gather(all_ms, mine_ms)
+        extra["rank_ms_with_stores"] = [float(x.item()) for x in all_ms]
         # the literal alternative: GEMM into the local block, then an NCCL all-gather of the blocks
         blk = torch.empty((rows, N), dtype=torch.bfloat16, device=dev)
         full = cmats[0].tensor
@@ -771,7 +815,7 @@ def run_ours(args):
         def nccl_step():
             ops.matmul_relu(a, b, out=blk)
             dist.all_gather_into_tensor(full, blk)
-        if M % world == 0:
+        if len({h - l for l, h in blocks}) == 1:      # the collective wants equal blocks
             extra["ms_per_step_gemm_then_nccl_allgather"] = time_steps(nccl_step, kn, 1, torch, dist) / kn
         del blk
     c_local = c_fulls[0][lo:hi]
@@ -863,12 +907,19 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(world, completion=(
-                None if completion is None else
-                "per-rank flags (st.release.sys by the launch's last CTA) + bounded device-side wait; "
-                + ("checked inside every step" if completion == "strict" else
-                   "the flags of step i are checked while step i+1 runs (two copies of C alternate), all outstanding flags inside the timed region")),
-                store=store, preheat_s=args.preheat_s),
+            "config": workload_config(world),
+            "run": {
+                "preheat": (f"untimed warm-up steps continue until {args.preheat_s:g} s of work have run, so that the timed steps "
+                            "see the steady power-capped clocks at every N"),
+                "completion": None if completion is None else (
+                    "per-rank flags (st.release.sys by the launch's last CTA) + bounded device-side wait; "
+                    + ("checked inside every step" if completion == "strict" else
+                       "the flags of step i are checked while step i+1 runs (two copies of C alternate), all outstanding flags "
+                       "inside the timed region")),
+                "allgather_store": store,
+                "row_blocks": None if world == 1 else ("equal" if rank_rates is None else
+                                                       "in proportion to each GPU's rate measured on an equal block before the timed steps"),
+            },
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches_timed, "clocks": clocks,
             "device_status": [status, status2], "others": others,
             "parity": "partial: the CPU nest the kernels are held to is pinned only by this repository's own float64 fixtures "
@@ -879,6 +930,10 @@ def run_ours(args):
             line["c1"] = c1
         if allgather_check is not None:
             line["allgather_check"] = allgather_check
+        if world > 1:
+            line["row_blocks"] = [list(x) for x in blocks]
+            if rank_rates is not None:
+                line["rank_rates_tflops_equal_blocks_no_stores"] = rank_rates
         if tf32_peak is not None:
             line["tf32_cublas_tflops_live"] = tf32_peak
         if cpu is not None:
@@ -902,6 +957,8 @@ def main():
                     help="N>1: when the other ranks' completion flags of a step are waited for")
     ap.add_argument("--peer-backend", choices=("auto", "ipc", "symmetric"), default="auto",
                     help="N>1: how the ranks' copies of C are made reachable (symmetric memory offers multicast)")
+    ap.add_argument("--equal-rows", action="store_true",
+                    help="N>1: equal row blocks instead of blocks in proportion to each GPU's measured rate")
     ap.add_argument("--no-multicast", action="store_true", help="N>1: unicast peer stores even when a multicast mapping exists")
     ap.add_argument("--preheat-s", type=float, default=2.0,
                     help="untimed warm-up continues until this many seconds of steps have run (0 = exactly --warmup steps)")

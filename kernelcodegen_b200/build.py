@@ -78,6 +78,27 @@ HOST_LIB_PATH = PKG_DIR / "libkcg_runtime.so"
 ROOT = PKG_DIR.parent
 
 
+def shared_libstdcxx(cxx: str) -> list[str]:
+    """Extra link inputs that make `cxx` link the C++ runtime dynamically.
+
+    Some toolchain installs ship a libstdc++.so link that points nowhere next to a libstdc++.a;
+    the linker then silently takes the archive, and every shared library built that way carries
+    (and exports) its own copy of the C++ runtime -- two such libraries in one process corrupt
+    each other's iostream state.  When the compiler's own libstdc++.so does not resolve, the
+    system's libstdc++.so.6 is named explicitly so that the archive is never consulted."""
+    try:
+        found = subprocess.run([cxx, "-print-file-name=libstdc++.so"], stdout=subprocess.PIPE, text=True).stdout.strip()
+    except OSError:
+        found = ""
+    if found and os.path.isabs(found) and os.path.exists(found):
+        return []
+    for cand in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/lib/x86_64-linux-gnu/libstdc++.so.6",
+                 "/usr/lib64/libstdc++.so.6", "/usr/lib/aarch64-linux-gnu/libstdc++.so.6"):
+        if os.path.exists(cand):
+            return [cand]
+    return []
+
+
 def host_sources() -> list[Path]:
     return sorted((ROOT / "src").rglob("*.cc"))
 
@@ -95,7 +116,7 @@ def build_host(force: bool = False) -> Path:
     tmp = HOST_LIB_PATH.with_suffix(".so.tmp")
     cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-I", str(ROOT / "include"),
            *map(str, host_sources()), "-o", str(tmp), "-L", str(PKG_DIR), "-lkcg_b200",
-           "-Wl,-rpath,$ORIGIN"]
+           "-Wl,-rpath,$ORIGIN", *shared_libstdcxx(cxx)]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout)
@@ -109,7 +130,8 @@ def compile_program(source: Path, output: Path, extra: list[str] | None = None) 
     build_host()
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
     cmd = [cxx, "-std=c++17", "-O1", "-I", str(ROOT / "include"), str(source), "-o", str(output),
-           "-L", str(PKG_DIR), "-lkcg_runtime", "-lkcg_b200", f"-Wl,-rpath,{PKG_DIR}", *(extra or [])]
+           "-L", str(PKG_DIR), "-lkcg_runtime", "-lkcg_b200", f"-Wl,-rpath,{PKG_DIR}", *shared_libstdcxx(cxx),
+           *(extra or [])]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"compiling {source} failed:\n{res.stdout}")

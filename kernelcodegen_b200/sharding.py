@@ -10,7 +10,7 @@ noticed on the host instead of by a kernel waiting on it.
 from __future__ import annotations
 
 import time
-from typing import Tuple
+from typing import List, Sequence, Tuple
 
 
 def row_block(m: int, rank: int, world: int, align: int = 128) -> Tuple[int, int]:
@@ -22,6 +22,38 @@ def row_block(m: int, rank: int, world: int, align: int = 128) -> Tuple[int, int
     lo_b = rank * base + min(rank, extra)
     hi_b = lo_b + base + (1 if rank < extra else 0)
     return min(lo_b * align, m), min(hi_b * align, m)
+
+
+def weighted_row_blocks(m: int, weights: Sequence[float], align: int = 128) -> List[Tuple[int, int]]:
+    """[lo, hi) rows of every rank when rank r should receive a share of the rows proportional to
+    weights[r] (for instance its measured rate: the GPUs of one node differ by several per cent
+    under their power caps, and a step ends when the slowest rank ends).  Blocks of `align` rows;
+    every rank receives at least one block while there are enough; equal weights give the split
+    of `row_block`."""
+    world = len(weights)
+    if world <= 0 or any((not w > 0) or w != w or w == float("inf") for w in weights):
+        raise ValueError("weights must be positive and finite")
+    blocks = (m + align - 1) // align
+    total = float(sum(weights))
+    ideal = [w / total * blocks for w in weights]
+    counts = [int(x) for x in ideal]
+    if blocks >= world:
+        counts = [max(1, c) for c in counts]
+    # hand the remaining blocks to the largest fractional parts (ties: lowest rank, like row_block);
+    # take back from the smallest if the minimum of one block per rank overshot
+    while sum(counts) < blocks:
+        r = max(range(world), key=lambda i: (ideal[i] - counts[i], -i))
+        counts[r] += 1
+    while sum(counts) > blocks:
+        r = max((i for i in range(world) if counts[i] > (1 if blocks >= world else 0)),
+                key=lambda i: (counts[i] - ideal[i], i))
+        counts[r] -= 1
+    out, lo = [], 0
+    for c in counts:
+        hi = lo + c
+        out.append((min(lo * align, m), min(hi * align, m)))
+        lo = hi
+    return out
 
 
 def bh_shard(batch_heads: int, rank: int, world: int) -> Tuple[int, int]:

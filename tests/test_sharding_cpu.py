@@ -28,6 +28,29 @@ def test_row_blocks_cover_and_align():
     assert sharding.row_block(32768, 3, 8) == (12288, 16384)
 
 
+def test_weighted_row_blocks():
+    # equal weights = the even split
+    for m in (128, 4096, 32768, 1000, 130):
+        for world in (1, 2, 4, 8):
+            assert sharding.weighted_row_blocks(m, [1.0] * world) == [sharding.row_block(m, r, world) for r in range(world)]
+    # a rank measured 10 % slower gets about 10 % fewer rows; the blocks still tile [0, m)
+    spans = sharding.weighted_row_blocks(32768, [1.0, 1.0, 0.9, 1.0, 1.0, 1.0, 1.0, 1.0])
+    assert spans[0][0] == 0 and spans[-1][1] == 32768
+    for (a, b), (c, d) in zip(spans, spans[1:]):
+        assert b == c
+    sizes = [hi - lo for lo, hi in spans]
+    assert all(s % 128 == 0 for s in sizes) and sum(sizes) == 32768
+    assert sizes[2] == min(sizes) and abs(sizes[2] / sizes[0] - 0.9) < 0.04
+    # finishing times are closer together than with the even split
+    rates = [1.0, 1.0, 0.9, 1.0, 1.0, 1.0, 1.0, 1.0]
+    assert max(s / r for s, r in zip(sizes, rates)) < max(4096 / r for r in rates)
+    # every rank keeps at least one block; fewer blocks than ranks leaves empty ranks at the end
+    assert all(hi > lo for lo, hi in sharding.weighted_row_blocks(1024, [100.0, 1.0, 1.0, 1.0]))
+    assert sharding.weighted_row_blocks(256, [1.0, 1.0, 1.0]) == [(0, 128), (128, 256), (256, 256)]
+    with pytest.raises(ValueError):
+        sharding.weighted_row_blocks(1024, [1.0, 0.0])
+
+
 def test_bh_shards():
     assert [sharding.bh_shard(256, r, 8) for r in range(8)] == [(32 * r, 32 * r + 32) for r in range(8)]
     assert [sharding.bh_shard(5, r, 2) for r in range(2)] == [(0, 3), (3, 5)]
