@@ -207,12 +207,17 @@ kcg_status_t kcg_transpose_launch(int64_t batch, int64_t rows, int64_t cols, int
                                   void* stream);
 
 /* The reference's BatchedMatmul operator on its own (src/Frontend/Operators.cc:253-420): `batch`
- * independent products described by `d`, operand i at base + i * stride (strides in elements;
- * 0 broadcasts an operand).  Layout::colMajor B = d->b_layout KCG_COL_MAJOR.  One GEMM launch per
- * batch entry on `stream`; the workspace is shared (the launches are stream-ordered). */
+ * independent products described by `d`, operand i at base + i * stride (strides in elements, each
+ * a multiple of 16 bytes; 0 shares an operand between all entries).  Layout::colMajor B =
+ * d->b_layout KCG_COL_MAJOR.  ONE launch: the batch entry is the outermost part of the persistent
+ * tile index and the third coordinate of the tensor maps, so tiles of all entries fill the SMs
+ * together and a ragged entry is zero-filled at its own edge.  For 3xTF32 the residual pass
+ * covers all entries in the same single launch, and a shared operand is split once; the
+ * workspace is sized by kcg_batched_gemm_workspace_bytes. */
 kcg_status_t kcg_batched_gemm_launch(const kcg_gemm_desc* d, int64_t batch, int64_t stride_a, int64_t stride_b,
                                      int64_t stride_c, const void* A, const void* B, void* C, void* workspace,
                                      size_t workspace_bytes, void* stream);
+size_t kcg_batched_gemm_workspace_bytes(const kcg_gemm_desc* d, int64_t batch, int64_t stride_a, int64_t stride_b);
 
 /* Host-buffer forms (what the reference's absent harness did around the kernel: cudaMalloc, H2D,
  * launch, D2H -- performance/output.log:6-13).  They allocate device buffers, copy, launch, copy

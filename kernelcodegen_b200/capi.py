@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "kcg_fmha_fwd_launch",
     "kcg_softmax_launch",
     "kcg_batched_gemm_launch",
+    "kcg_batched_gemm_workspace_bytes",
     "kcg_transpose_launch",
     "kcg_gemm_host",
     "kcg_gemm_host_staged",
@@ -132,6 +133,8 @@ def load() -> ctypes.CDLL:
     lib.kcg_batched_gemm_launch.restype = c_int
     lib.kcg_batched_gemm_launch.argtypes = [POINTER(GemmDesc), c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_size_t, c_void_p]
+    lib.kcg_batched_gemm_workspace_bytes.restype = c_size_t
+    lib.kcg_batched_gemm_workspace_bytes.argtypes = [POINTER(GemmDesc), c_int64, c_int64, c_int64]
     lib.kcg_transpose_launch.restype = c_int
     lib.kcg_transpose_launch.argtypes = [c_int64, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_void_p]
     lib.kcg_gemm_host.restype = c_int

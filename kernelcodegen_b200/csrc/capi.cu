@@ -154,18 +154,12 @@ kcg_status_t kcg_transpose_launch(int64_t batch, int64_t rows, int64_t cols, int
 kcg_status_t kcg_batched_gemm_launch(const kcg_gemm_desc* d, int64_t batch, int64_t stride_a, int64_t stride_b,
                                      int64_t stride_c, const void* A, const void* B, void* C, void* workspace,
                                      size_t workspace_bytes, void* stream) {
-  if (!d || !A || !B || !C) return KCG_BAD_ARGUMENT;
-  if (batch <= 0 || stride_a < 0 || stride_b < 0 || stride_c < 0) return KCG_BAD_SHAPE;
-  const size_t es = d->dtype_in == KCG_BF16 ? 2 : 4, os = d->dtype_out == KCG_BF16 ? 2 : 4;
-  for (int64_t i = 0; i < batch; ++i) {
-    const kcg_status_t st = gemm_launch_impl(
-        d, static_cast<const uint8_t*>(A) + static_cast<size_t>(i) * stride_a * es,
-        static_cast<const uint8_t*>(B) + static_cast<size_t>(i) * stride_b * es,
-        static_cast<uint8_t*>(C) + static_cast<size_t>(i) * stride_c * os, workspace, workspace_bytes,
-        static_cast<cudaStream_t>(stream));
-    if (st != KCG_OK) return st;
-  }
-  return KCG_OK;
+  return gemm_batched_launch_impl(d, batch, stride_a, stride_b, stride_c, A, B, C, workspace, workspace_bytes,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+size_t kcg_batched_gemm_workspace_bytes(const kcg_gemm_desc* d, int64_t batch, int64_t stride_a, int64_t stride_b) {
+  return gemm_batched_workspace_impl(d, batch, stride_a, stride_b);
 }
 
 kcg_status_t kcg_fmha_fwd_launch(const kcg_fmha_desc* d, const void* Q, const void* K,

@@ -39,6 +39,10 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
                               void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t gemm_workspace_impl(const kcg_gemm_desc* d);
+size_t gemm_batched_workspace_impl(const kcg_gemm_desc* d, long long batch, long long stride_a, long long stride_b);
+kcg_status_t gemm_batched_launch_impl(const kcg_gemm_desc* d, long long batch, long long stride_a, long long stride_b,
+                                      long long stride_c, const void* A, const void* B, void* C, void* ws,
+                                      size_t ws_bytes, cudaStream_t stream);
 kcg_status_t gemm_launch_geometry_impl(const kcg_gemm_desc* d, int* out);
 kcg_status_t fmha_launch_geometry_impl(const kcg_fmha_desc* d, int* out);
 int gemm_shared_k_tiles_impl(const kcg_gemm_desc* d);

@@ -50,6 +50,12 @@ struct GemmParams {
   int relu;
   int* status;
   uint32_t spin;
+  // Batched product: `batch` independent M x N x K products; tile index = batch entry major.  The
+  // operands are 3-D tensor maps {k, rows, batch}; an operand shared by all entries has batch
+  // extent 1 (a_bz / b_bz = 0: its batch coordinate stays 0).  C of entry b starts c_bstride
+  // elements after that of entry b - 1.
+  int batch, a_bz, b_bz;
+  long long c_bstride;
   int n_peers;
   void* peers[8];
   // Multicast form of the fused all-gather: when set, full 128-byte row segments are stored once
@@ -139,7 +145,7 @@ struct GemmCfg {
 // floats, laid out as write_partial leaves them).  They are added in slot order, so the result
 // does not depend on which contributor happens to finish last.
 template <int BN, typename OutT>
-__device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, int row0, int col0,
+__device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, int row0, int col0, long long c_off,
                                            uint8_t* epi_stage, int lane, const float* sk_src = nullptr,
                                            int sk_n = 0, int sk_own = 0) {
       // Each pass handles CW columns = 128 bytes of output per row: thread t (row t of the
@@ -228,7 +234,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
             }
           } else if (row0 + lane < p.M) {
             // ragged right edge: element-wise, this thread's row
-            const long long off = static_cast<long long>(row0 + lane) * p.ldc + col + sub * 32;
+            const long long off = c_off + static_cast<long long>(row0 + lane) * p.ldc + col + sub * 32;
             for (int dst = 0; dst <= p.n_peers; ++dst) {
               OutT* cp = static_cast<OutT*>(dst == 0 ? p.C : p.peers[dst - 1]) + off;
               for (int i = 0; i < 32; ++i) {
@@ -255,7 +261,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
               if (grow < p.M) {
                 const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
                                                                  ((ch ^ (rloc & 7)) << 4));
-                multimem_st_v4(cbase + (static_cast<long long>(grow) * p.ldc + col) *
+                multimem_st_v4(cbase + (c_off + static_cast<long long>(grow) * p.ldc + col) *
                                            static_cast<long long>(sizeof(OutT)) +
                                    ch * 16, v);
               }
@@ -270,7 +276,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
               if (grow < p.M) {
                 const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
                                                                  ((ch ^ (rloc & 7)) << 4));
-                *reinterpret_cast<uint4*>(cbase + (static_cast<long long>(grow) * p.ldc + col) *
+                *reinterpret_cast<uint4*>(cbase + (c_off + static_cast<long long>(grow) * p.ldc + col) *
                                                       static_cast<long long>(sizeof(OutT)) +
                                           ch * 16) = v;
               }
@@ -380,11 +386,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_entry = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_entry * p.batch;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_per_group = p.group_m * p.tiles_n;
 
-  auto tile_coord = [&](int t, int& mb, int& nb) {
+  auto tile_coord = [&](int t, int& mb, int& nb, int& bt) {
+    bt = t / tiles_per_entry;
+    t -= bt * tiles_per_entry;
     const int g = t / tiles_per_group;
     const int first_m = g * p.group_m;
     const int gm = min(p.group_m, p.tiles_m - first_m);
@@ -403,9 +412,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // beside its tail (programmatic dependent launch)
       if (KIND == 2) griddep_wait();
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int mb, nb;
-        tile_coord(t, mb, nb);
+        int mb, nb, bt;
+        tile_coord(t, mb, nb, bt);
         const int m0 = mb * BM, n0 = nb * BN;
+        const int za = bt * p.a_bz, zb = bt * p.b_bz;
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status,
                          DEV_TIMEOUT_PRODUCER, p.spin);
@@ -415,17 +425,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t sB = sA + Cfg::NOPS * A_BYTES;
           mbar_expect_tx(full, STAGE_BYTES);
           const int k0 = kb * BK;
-          tma_load_2d(sA, &tmA, full, k0, m0);
-          if (KIND == 2) tma_load_2d(sA + A_BYTES, &tmA2, full, k0, m0);
+          tma_load_3d(sA, &tmA, full, k0, m0, za);
+          if (KIND == 2) tma_load_3d(sA + A_BYTES, &tmA2, full, k0, m0, za);
           if (B_KMAJOR) {
-            tma_load_2d(sB, &tmB, full, k0, n0);
-            if (KIND == 2) tma_load_2d(sB + B_BYTES, &tmB2, full, k0, n0);
+            tma_load_3d(sB, &tmB, full, k0, n0, zb);
+            if (KIND == 2) tma_load_3d(sB + B_BYTES, &tmB2, full, k0, n0, zb);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / B_NGROUP; ++j) {
-              tma_load_2d(sB + j * B_GROUP, &tmB, full, n0 + j * B_NGROUP, k0);
+              tma_load_3d(sB + j * B_GROUP, &tmB, full, n0 + j * B_NGROUP, k0, zb);
               if (KIND == 2)
-                tma_load_2d(sB + B_BYTES + j * B_GROUP, &tmB2, full, n0 + j * B_NGROUP, k0);
+                tma_load_3d(sB + B_BYTES + j * B_GROUP, &tmB2, full, n0 + j * B_NGROUP, k0, zb);
             }
           }
           if (++stage == STAGES) {
@@ -529,8 +539,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
       const int acc = local & 1;
       if (acc != grp) continue;
-      int mb, nb;
-      tile_coord(t, mb, nb);
+      int mb, nb, bt;
+      tile_coord(t, mb, nb, bt);
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE,
                      p.spin);
@@ -538,7 +548,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       const int row0 = mb * BM + q * 32;           // first row of this warp's 32-row slab
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      drain_tile<BN, OutT>(p, t_row, row0, nb * BN, epi_stage, lane);
+      drain_tile<BN, OutT>(p, t_row, row0, nb * BN, bt * p.c_bstride, epi_stage, lane);
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
     }
@@ -646,10 +656,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_holder;
 
   const int tiles_m2 = (p.M + 2 * BM - 1) / (2 * BM);
-  const int num_tiles = tiles_m2 * p.tiles_n;
+  const int tiles_per_entry = tiles_m2 * p.tiles_n;
+  const int num_tiles = tiles_per_entry * p.batch;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_per_group = p.group_m * p.tiles_n;
-  auto tile_coord = [&](int t, int& mb, int& nb) {
+  auto tile_coord = [&](int t, int& mb, int& nb, int& bt) {
+    bt = t / tiles_per_entry;
+    t -= bt * tiles_per_entry;
     const int g = t / tiles_per_group;
     const int first_m = g * p.group_m;
     const int gm = min(p.group_m, tiles_m2 - first_m);
@@ -668,10 +681,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       WorkIter it(p, pair, num_pairs, num_tiles, num_kb);
       WorkItem w;
       while (ok && it.next(w)) {
-        int mb, nb;
-        tile_coord(w.t, mb, nb);
+        int mb, nb, bt;
+        tile_coord(w.t, mb, nb, bt);
         const int m0 = mb * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = nb * BN + static_cast<int>(rank) * BNL;
+        const int za = bt * p.a_bz, zb = bt * p.b_bz;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER, p.spin);
           if (!ok) break;
@@ -680,16 +694,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sB = sA + Cfg::NOPS * A_BYTES;
           if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * STAGE_BYTES);
           const int k0 = kb * BK;
-          tma_load_2d_pair(sA, &tmA, full, k0, m0);
-          if (KIND == 2) tma_load_2d_pair(sA + A_BYTES, &tmA2, full, k0, m0);
+          tma_load_3d_pair(sA, &tmA, full, k0, m0, za);
+          if (KIND == 2) tma_load_3d_pair(sA + A_BYTES, &tmA2, full, k0, m0, za);
           if (B_KMAJOR) {
-            tma_load_2d_pair(sB, &tmB, full, k0, n0);
-            if (KIND == 2) tma_load_2d_pair(sB + B_BYTES, &tmB2, full, k0, n0);
+            tma_load_3d_pair(sB, &tmB, full, k0, n0, zb);
+            if (KIND == 2) tma_load_3d_pair(sB + B_BYTES, &tmB2, full, k0, n0, zb);
           } else {
 #pragma unroll
             for (int j = 0; j < BNL / B_NGROUP; ++j) {
-              tma_load_2d_pair(sB + j * B_GROUP, &tmB, full, n0 + j * B_NGROUP, k0);
-              if (KIND == 2) tma_load_2d_pair(sB + B_BYTES + j * B_GROUP, &tmB2, full, n0 + j * B_NGROUP, k0);
+              tma_load_3d_pair(sB + j * B_GROUP, &tmB, full, n0 + j * B_NGROUP, k0, zb);
+              if (KIND == 2) tma_load_3d_pair(sB + B_BYTES + j * B_GROUP, &tmB2, full, n0 + j * B_NGROUP, k0, zb);
             }
           }
           if (++stage == STAGES) {
@@ -803,8 +817,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     WorkIter it(p, pair, num_pairs, num_tiles, num_kb);
     WorkItem w;
     for (; ok && it.next(w); ++local) {
-      int mb, nb;
-      tile_coord(w.t, mb, nb);
+      int mb, nb, bt;
+      tile_coord(w.t, mb, nb, bt);
+      const long long c_off = bt * p.c_bstride;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE, p.spin);
@@ -813,7 +828,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row0 = mb * 2 * BM + static_cast<int>(rank) * BM + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       if (w.kb1 - w.kb0 == num_kb) {
-        drain_tile<BN, OutT>(p, t_row, row0, nb * BN, epi_stage, lane);
+        drain_tile<BN, OutT>(p, t_row, row0, nb * BN, c_off, epi_stage, lane);
       } else {
         // Part of a tile's K range.  Every contributor leaves its partial slab in global memory and
         // counts itself in; nobody waits: whoever finds all the others already counted adds the
@@ -831,7 +846,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) seen = atom_add_acq_rel_gpu(p.sk_count + slab, 1);
         seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
         if (seen == n_contrib - 1) {
-          drain_tile<BN, OutT>(p, t_row, row0, nb * BN, epi_stage, lane, slab_base, n_contrib, pair - first);
+          drain_tile<BN, OutT>(p, t_row, row0, nb * BN, c_off, epi_stage, lane, slab_base, n_contrib, pair - first);
           if (lane == 0) p.sk_count[slab] = 0;   // ready for the next launch
         }
       }
@@ -858,9 +873,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 struct SplitArgs {
   const float* src;
   float* lo;
-  long long rows;
+  long long rows;     // rows of all batch entries together (batch * rows per entry)
   int cols4;
   long long ld;
+  long long rows_per_entry;
+  long long entry_stride;   // elements between the first rows of successive entries in src
 };
 __device__ __forceinline__ float4 tf32_residual(const float4 v) {
   float4 l;
@@ -879,7 +896,9 @@ __global__ void __launch_bounds__(256) split_lo_kernel(SplitArgs a, SplitArgs b)
     const SplitArgs& s = second ? b : a;
     const long long k = second ? i - na : i;
     const long long r = k / s.cols4;
-    return reinterpret_cast<const float4*>(s.src + r * s.ld + 4ll * (k - r * s.cols4));
+    const long long e = r / s.rows_per_entry;
+    return reinterpret_cast<const float4*>(s.src + e * s.entry_stride + (r - e * s.rows_per_entry) * s.ld +
+                                           4ll * (k - r * s.cols4));
   };
   auto dst_of = [&](long long i) -> float4* {
     return i >= na ? reinterpret_cast<float4*>(b.lo) + (i - na) : reinterpret_cast<float4*>(a.lo) + i;
@@ -1009,8 +1028,8 @@ kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const
   static_assert(smem <= SMEM_LIMIT, "shared memory budget");
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int sms = device_sm_count();
-  const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sms ? tiles : sms;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batch;
+  const int grid = tiles < sms ? static_cast<int>(tiles) : sms;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1055,7 +1074,7 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
   constexpr int smem = STAGES * Cfg::STAGE_BYTES + Cfg::CTRL_BYTES + Cfg::EPI_BYTES + 1024;
   static_assert(smem <= SMEM_LIMIT, "shared memory budget");
   KCG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * p.tiles_n * p.batch;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1119,8 +1138,9 @@ kcg_status_t dispatch_pair_shape(int bn, bool b_kmajor, const CUtensorMap& tA, c
 //    3xTF32 with 128-wide tiles +15..30 % on 4096x2048x1024 and 4096^3);
 //  - long launches are power-limited, and there the pair kernel sustains lower clocks
 //    (bf16 16384^3 -3.5 %, 32768^3 -19 %), so single CTAs with 256-wide tiles are used.
-static void resolve_variant(const kcg_gemm_desc* d, int* bn, bool* pair_mode) {
-  const double work = 2.0 * static_cast<double>(d->M) * static_cast<double>(d->N) * static_cast<double>(d->K);
+static void resolve_variant(const kcg_gemm_desc* d, int* bn, bool* pair_mode, long long batch = 1) {
+  const double work = 2.0 * static_cast<double>(d->M) * static_cast<double>(d->N) * static_cast<double>(d->K) *
+                      static_cast<double>(batch);
   const bool small_job = work < 4e12;
   *bn = d->tile_n;
   if (*bn == 0) *bn = (d->precision == KCG_PREC_3XTF32 && small_job) ? 128 : 256;
@@ -1213,11 +1233,43 @@ size_t gemm_workspace_impl(const kcg_gemm_desc* d) {
   return need;
 }
 
-kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
-                              void* ws, size_t ws_bytes, cudaStream_t stream) {
+// bytes of the residual arrays of a batched 3xTF32 product: an operand shared by all entries
+// (stride 0) is split once
+static size_t batched_lo_bytes(const kcg_gemm_desc* d, long long batch, long long stride_a, long long stride_b) {
+  if (d->precision != KCG_PREC_3XTF32) return 0;
+  const size_t ea = stride_a == 0 ? 1 : static_cast<size_t>(batch), eb = stride_b == 0 ? 1 : static_cast<size_t>(batch);
+  return pad256(ea * d->M * d->K * 4) + pad256(eb * d->K * d->N * 4);
+}
+
+size_t gemm_batched_workspace_impl(const kcg_gemm_desc* d, long long batch, long long stride_a, long long stride_b) {
+  if (!d || batch <= 0) return 0;
+  if (batch == 1) return gemm_workspace_impl(d);
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
+  if (d->M > 0x7FFFFFFF || d->N > 0x7FFFFFFF || d->K > 0x7FFFFFFF) return 0;
+  size_t need = batched_lo_bytes(d, batch, stride_a, stride_b);
+  int bn = 0;
+  bool pair_mode = false;
+  resolve_variant(d, &bn, &pair_mode, batch);
+  if (pair_mode && (bn == 128 || bn == 256)) {
+    const int bk = d->precision == KCG_PREC_BF16 ? 64 : 32;
+    const long long tiles = ((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * batch;
+    if (tiles <= 0x7FFFFFFF)
+      need += plan_shared_k(static_cast<int>(tiles), static_cast<int>((d->K + bk - 1) / bk), 74, bn).bytes;
+  }
+  return need;
+}
+
+// `batch` independent products described by `d`; operand i at base + i * stride (elements; 0 = the
+// operand is shared).  One launch: the batch entry is the outermost part of the tile index and the
+// third coordinate of the tensor maps, so a tile never runs into the next entry's rows and ragged
+// shapes are zero-filled per entry.
+kcg_status_t gemm_batched_launch_impl(const kcg_gemm_desc* d, long long batch, long long stride_a, long long stride_b,
+                                      long long stride_c, const void* A, const void* B, void* C, void* ws,
+                                      size_t ws_bytes, cudaStream_t stream) {
   if (!d || !A || !B || !C) return KCG_BAD_ARGUMENT;
   if (d->M <= 0 || d->N <= 0 || d->K <= 0) return KCG_BAD_SHAPE;
   if (d->M > 0x7FFFFFFF || d->N > 0x7FFFFFFF || d->K > 0x7FFFFFFF) return KCG_BAD_SHAPE;
+  if (batch <= 0 || batch > 0x7FFFFFFF || stride_a < 0 || stride_b < 0 || stride_c < 0) return KCG_BAD_SHAPE;
   const bool b_kmajor = d->b_layout == KCG_COL_MAJOR;
   if (d->b_layout != KCG_ROW_MAJOR && d->b_layout != KCG_COL_MAJOR) return KCG_UNSUPPORTED;
   if (d->lda < d->K || d->ldc < d->N || d->ldb < (b_kmajor ? d->K : d->N)) return KCG_BAD_SHAPE;
@@ -1238,6 +1290,12 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   const int os = d->dtype_out == KCG_BF16 ? 2 : 4;
   if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return KCG_BAD_ALIGN;
   if ((d->lda * es) % 16 || (d->ldb * es) % 16 || (d->ldc * os) % 16) return KCG_BAD_ALIGN;
+  if (batch > 1) {
+    if ((stride_a * es) % 16 || (stride_b * es) % 16 || (stride_c * os) % 16) return KCG_BAD_ALIGN;
+    if (stride_c == 0) return KCG_BAD_SHAPE;      // every entry needs its own C
+  }
+  const long long batch_a = (batch > 1 && stride_a != 0) ? batch : 1;
+  const long long batch_b = (batch > 1 && stride_b != 0) ? batch : 1;
   for (int i = 0; i < d->n_peers; ++i)
     if (!d->peer_c[i] || !aligned16(d->peer_c[i])) return KCG_BAD_ALIGN;
   if (d->mc_c) {
@@ -1249,9 +1307,13 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
     if (!d->done_flags[i] || (reinterpret_cast<uintptr_t>(d->done_flags[i]) & 3u)) return KCG_BAD_ALIGN;
   int bn = 0;
   bool pair_mode = false;
-  resolve_variant(d, &bn, &pair_mode);
+  resolve_variant(d, &bn, &pair_mode, batch);
   if (bn != 128 && bn != 256) return KCG_UNSUPPORTED;
   if (d->cta_group != 0 && d->cta_group != 1 && d->cta_group != 2) return KCG_UNSUPPORTED;
+  {
+    const long long tm = pair_mode ? (d->M + 2 * BM - 1) / (2 * BM) : (d->M + BM - 1) / BM;
+    if (tm * ((d->N + bn - 1) / bn) * batch > 0x7FFFFFFFll) return KCG_BAD_SHAPE;
+  }
 
   const void* pa = A;
   const void* pb = B;
@@ -1259,18 +1321,21 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   const void* pb2 = B;
   long long lda = d->lda, ldb = d->ldb;
   long long lda2 = d->lda, ldb2 = d->ldb;  // leading dimensions of the residual arrays
+  long long sa_elems = stride_a, sb_elems = stride_b;      // entry strides of the operands ...
+  long long sa2_elems = stride_a, sb2_elems = stride_b;    // ... and of the residual arrays
+  const size_t lo_bytes = batched_lo_bytes(d, batch, batch_a == 1 ? 0 : stride_a, batch_b == 1 ? 0 : stride_b);
   if (kind == 2) {
-    const size_t need = gemm_lo_bytes(d);
+    const size_t need = lo_bytes;
     if (!ws || ws_bytes < need || !aligned16(ws)) return KCG_BAD_WORKSPACE;
     if ((d->K % 4) || (d->N % 4)) return KCG_BAD_ALIGN;
-    const size_t a = pad256(static_cast<size_t>(d->M) * d->K * 4);
+    const size_t a = pad256(static_cast<size_t>(batch_a) * d->M * d->K * 4);
     float* a_lo = static_cast<float*>(ws);
     float* b_lo = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + a);
     const int sms = device_sm_count();
     const long long b_rows = b_kmajor ? d->N : d->K;
     const long long b_cols = b_kmajor ? d->K : d->N;
-    SplitArgs sa{static_cast<const float*>(A), a_lo, d->M, static_cast<int>(d->K / 4), d->lda};
-    SplitArgs sb{static_cast<const float*>(B), b_lo, b_rows, static_cast<int>(b_cols / 4), d->ldb};
+    SplitArgs sa{static_cast<const float*>(A), a_lo, batch_a * d->M, static_cast<int>(d->K / 4), d->lda, d->M, stride_a};
+    SplitArgs sb{static_cast<const float*>(B), b_lo, batch_b * b_rows, static_cast<int>(b_cols / 4), d->ldb, b_rows, stride_b};
     split_lo_kernel<<<sms * 4, 256, 0, stream>>>(sa, sb);
     g_launches.fetch_add(1);
     KCG_CUDA_TRY(cudaGetLastError());
@@ -1278,7 +1343,12 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
     pb2 = b_lo;
     lda2 = d->K;
     ldb2 = b_cols;
+    sa2_elems = d->M * d->K;
+    sb2_elems = b_rows * b_cols;
   }
+  // entry strides of the tensor maps (any valid value when the operand has a single entry)
+  if (batch_a == 1) sa_elems = sa2_elems = d->M * lda;
+  if (batch_b == 1) sb_elems = sb2_elems = (b_kmajor ? d->N : d->K) * ldb;
 
   using Cfg0 = GemmCfg<0, 128>;
   (void)sizeof(Cfg0);
@@ -1287,18 +1357,20 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   const uint32_t bk = 128 / es;
   CUtensorMap tA, tB, tA2, tB2;
   {
-    const uint64_t dims[2] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->M)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * es};
-    const uint64_t strides2[1] = {static_cast<uint64_t>(lda2) * es};
-    const uint32_t box[2] = {bk, BM};
-    kcg_status_t st = encode_tmap(&tA, dt, 2, pa, dims, strides, box);
+    const uint64_t dims[3] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->M), static_cast<uint64_t>(batch_a)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(lda) * es, static_cast<uint64_t>(sa_elems) * es};
+    const uint64_t strides2[2] = {static_cast<uint64_t>(lda2) * es, static_cast<uint64_t>(sa2_elems) * es};
+    const uint32_t box[3] = {bk, BM, 1};
+    kcg_status_t st = encode_tmap(&tA, dt, 3, pa, dims, strides, box);
     if (st != KCG_OK) return st;
-    st = encode_tmap(&tA2, dt, 2, pa2, dims, strides2, box);
+    st = encode_tmap(&tA2, dt, 3, pa2, dims, strides2, box);
     if (st != KCG_OK) return st;
   }
   {
-    uint64_t dims[2];
-    uint32_t box[2];
+    uint64_t dims[3];
+    uint32_t box[3];
+    dims[2] = static_cast<uint64_t>(batch_b);
+    box[2] = 1;
     if (b_kmajor) {  // B stored [N, K]
       dims[0] = d->K;
       dims[1] = d->N;
@@ -1310,13 +1382,13 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
       box[0] = 128 / es;
       box[1] = bk;
     }
-    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * es};
+    const uint64_t strides[2] = {static_cast<uint64_t>(ldb) * es, static_cast<uint64_t>(sb_elems) * es};
     const CUtensorMapSwizzle sw = (!b_kmajor && es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                          : CU_TENSOR_MAP_SWIZZLE_128B;
-    const uint64_t strides2[1] = {static_cast<uint64_t>(ldb2) * es};
-    kcg_status_t st = encode_tmap(&tB, dt, 2, pb, dims, strides, box, sw);
+    const uint64_t strides2[2] = {static_cast<uint64_t>(ldb2) * es, static_cast<uint64_t>(sb2_elems) * es};
+    kcg_status_t st = encode_tmap(&tB, dt, 3, pb, dims, strides, box, sw);
     if (st != KCG_OK) return st;
-    st = encode_tmap(&tB2, dt, 2, pb2, dims, strides2, box, sw);
+    st = encode_tmap(&tB2, dt, 3, pb2, dims, strides2, box, sw);
     if (st != KCG_OK) return st;
   }
 
@@ -1326,6 +1398,10 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   p.N = static_cast<int>(d->N);
   p.K = static_cast<int>(d->K);
   p.ldc = d->ldc;
+  p.batch = static_cast<int>(batch);
+  p.a_bz = batch_a > 1 ? 1 : 0;
+  p.b_bz = batch_b > 1 ? 1 : 0;
+  p.c_bstride = batch > 1 ? stride_c : 0;
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + bn - 1) / bn;
   p.group_m = d->group_m > 0 ? d->group_m : 16;
@@ -1353,7 +1429,6 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
 
   if (pair_mode) {
     // what follows the residual arrays in the workspace is free for the shared-K tail
-    const size_t lo_bytes = gemm_lo_bytes(d);
     void* sk_ws = (ws && aligned16(ws) && ws_bytes > lo_bytes) ? static_cast<uint8_t*>(ws) + lo_bytes : nullptr;
     const size_t sk_bytes = sk_ws ? ws_bytes - lo_bytes : 0;
     if (kind == 0) {
@@ -1374,6 +1449,11 @@ kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void*
   }
   if (kind == 1) return dispatch_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
   return dispatch_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+}
+
+kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,
+                              void* ws, size_t ws_bytes, cudaStream_t stream) {
+  return gemm_batched_launch_impl(d, 1, 0, 0, 0, A, B, C, ws, ws_bytes, stream);
 }
 
 // Device address of g_static_scratch on the current device.  Looked up once per device, with

@@ -260,7 +260,7 @@ def batched_matmul(a: torch.Tensor, b: torch.Tensor, *, b_col_major: bool = Fals
     d.b_layout = capi.KCG_COL_MAJOR if b_col_major else capi.KCG_ROW_MAJOR
     lib = capi.load()
     with torch.cuda.device(dev):
-        ws_bytes = lib.kcg_gemm_workspace_bytes(ctypes.byref(d))
+        ws_bytes = lib.kcg_batched_gemm_workspace_bytes(ctypes.byref(d), batch, m * k, k * n)
         ws = _workspace(dev, ws_bytes)
         st = lib.kcg_batched_gemm_launch(ctypes.byref(d), batch, m * k, k * n, m * n, a.data_ptr(), b.data_ptr(),
                                          out.data_ptr(), ws.data_ptr() if ws is not None else None, ws_bytes,

@@ -196,7 +196,8 @@ size_t workspaceBytes(mlir::ModuleOp& module) {
   for (auto& p : planLaunches(module)) {
     if (p.status != KCG_OK) continue;
     size_t n = 0;
-    if (p.kind == LaunchPlan::Kind::Gemm || p.kind == LaunchPlan::Kind::BatchedGemm) n = kcg_gemm_workspace_bytes(&p.gemm);
+    if (p.kind == LaunchPlan::Kind::Gemm) n = kcg_gemm_workspace_bytes(&p.gemm);
+    else if (p.kind == LaunchPlan::Kind::BatchedGemm) n = kcg_batched_gemm_workspace_bytes(&p.gemm, p.batch, p.strideA, p.strideB);
     else if (p.kind == LaunchPlan::Kind::Fmha) n = kcg_fmha_workspace_bytes(&p.fmha);
     need = n > need ? n : need;
   }

@@ -62,6 +62,57 @@ def test_batched_matmul_matches_oracle(cuda_device, b_col_major):
     assert ops.last_device_status() == 0
 
 
+@pytest.mark.parametrize("batch,m,n,k", [(64, 128, 128, 64), (5, 300, 72, 40), (3, 130, 260, 132), (17, 64, 8, 8)])
+@pytest.mark.parametrize("precision,tol", [("3xtf32", 1e-4), ("tf32", 5e-3)])
+def test_batched_matmul_one_launch_many_entries(cuda_device, batch, m, n, k, precision, tol):
+    """All entries go through one launch (batch = third tensor-map coordinate): ragged entries
+    must not read their neighbours' rows, and the launch count says it was one GEMM launch."""
+    from kernelcodegen_b200 import ops
+
+    g = torch.Generator().manual_seed(batch * 1000 + m)
+    a = torch.rand((batch, m, k), generator=g) * 2 - 1
+    b = torch.rand((batch, k, n), generator=g) * 2 - 1
+    want = oracle.batched_matmul(a.numpy(), b.numpy())
+    before = ops.launch_count()
+    got = ops.batched_matmul(a.to(cuda_device), b.to(cuda_device), precision=precision)
+    launches = ops.launch_count() - before
+    assert launches == (2 if precision == "3xtf32" else 1)      # residual pass + GEMM, or the GEMM alone
+    assert rel_err(got.cpu().numpy(), want) <= tol
+    assert ops.last_device_status() == 0
+
+
+def test_batched_matmul_shared_operand(cuda_device):
+    """stride 0: one B for every entry (split once for 3xTF32), through the C-ABI."""
+    import ctypes
+
+    from kernelcodegen_b200 import capi
+
+    lib = capi.load()
+    batch, m, n, k = 6, 200, 136, 72
+    g = torch.Generator().manual_seed(9)
+    a = (torch.rand((batch, m, k), generator=g) * 2 - 1).to(cuda_device)
+    b = (torch.rand((k, n), generator=g) * 2 - 1).to(cuda_device)
+    c = torch.full((batch, m, n), float("nan"), device=cuda_device)
+    d = capi.GemmDesc()
+    d.M, d.N, d.K = m, n, k
+    d.lda, d.ldb, d.ldc = k, n, n
+    d.dtype_in = d.dtype_out = capi.KCG_F32
+    d.precision = capi.KCG_PREC_3XTF32
+    need = lib.kcg_batched_gemm_workspace_bytes(ctypes.byref(d), batch, m * k, 0)
+    assert need >= 4 * (batch * m * k + k * n)
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda_device)
+    st = lib.kcg_batched_gemm_launch(ctypes.byref(d), batch, m * k, 0, m * n, a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                     ws.data_ptr(), need, None)
+    assert st == capi.KCG_OK, capi.status_str(st)
+    torch.cuda.synchronize()
+    want = np.stack([oracle.matmul(a[i].cpu().numpy(), b.cpu().numpy()) for i in range(batch)])
+    assert rel_err(c.cpu().numpy(), want) <= 1e-4
+    # an entry stride that is not a multiple of 16 bytes is refused
+    st = lib.kcg_batched_gemm_launch(ctypes.byref(d), batch, m * k + 1, 0, m * n, a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                     ws.data_ptr(), need, None)
+    assert st == capi.KCG_BAD_ALIGN
+
+
 def test_unfused_attention_graph_equals_fused_kernel(cuda_device):
     """BatchedMatmul(Q, K^T) -> Softmax -> BatchedMatmul(P, V) run operator by operator gives the
     fused FMHA kernel's answer (to the bf16 bar of the fused kernel)."""
