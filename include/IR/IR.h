@@ -51,6 +51,8 @@ struct Type {
   bool isMemRef() const { return memref; }
   bool isNone() const { return elem == ScalarKind::None; }
   Type elementType() const { return scalar(elem); }
+  Type getElementType() const { return scalar(elem); }
+  template <class T> T dyn_cast() const { return *this; }   // `type.dyn_cast<mlir::MemRefType>()` keeps compiling
   const std::vector<int64_t>& getShape() const { return shape; }
   int getMemorySpace() const { return memorySpace; }
   std::string str() const;
@@ -101,13 +103,96 @@ struct IndexExpr {
   void simplify();
 };
 
+// Quasi-affine expression: sums, products with constants, floordiv and mod by constants over
+// leaves that are either map dimensions (d0, d1, ...; the form user code builds, as with MLIR's
+// AffineExpr) or SSA values (the form stored on operations, after a map has been applied to its
+// operands).  Cheap to copy (shared immutable nodes); constants are folded on construction.
+class AffineExpr {
+ public:
+  enum class Kind { Cst, Dim, Val, Add, Mul, FloorDiv, Mod };
+  AffineExpr();                                   // the constant 0
+  static AffineExpr constant(int64_t c);
+  static AffineExpr dim(unsigned position);
+  static AffineExpr value(Value v);
+  static AffineExpr fromLinear(const IndexExpr& e);
+
+  AffineExpr operator+(const AffineExpr& o) const;
+  AffineExpr operator+(int64_t c) const { return *this + constant(c); }
+  AffineExpr operator-(int64_t c) const { return *this + constant(-c); }
+  AffineExpr operator*(const AffineExpr& o) const;   // one side must be a constant
+  AffineExpr operator*(int64_t c) const;
+  AffineExpr floorDiv(int64_t c) const;
+  AffineExpr floorDiv(uint64_t c) const { return floorDiv(static_cast<int64_t>(c)); }
+  AffineExpr floorDiv(int c) const { return floorDiv(static_cast<int64_t>(c)); }
+  AffineExpr operator%(int64_t c) const;
+  AffineExpr operator%(uint64_t c) const { return *this % static_cast<int64_t>(c); }
+  AffineExpr operator%(int c) const { return *this % static_cast<int64_t>(c); }
+
+  Kind kind() const;
+  int64_t constantValue() const;                  // Cst
+  unsigned dimPosition() const;                   // Dim
+  Value leafValue() const;                        // Val
+  bool isConstant() const { return kind() == Kind::Cst; }
+  AffineExpr lhs() const;                         // Add / Mul / FloorDiv / Mod: the (left) operand
+  AffineExpr rhs() const;                         // Add: the right operand; Mul / FloorDiv / Mod: the constant
+
+  // dims -> the given expressions (application of a map to operands, composition of maps)
+  AffineExpr replaceDims(const std::vector<AffineExpr>& by) const;
+  // every leaf equal to `from` -> `to`
+  AffineExpr replaceValue(Value from, const AffineExpr& to) const;
+  // leaves remapped through `fn` (cloning)
+  AffineExpr mapValues(const std::function<Value(Value)>& fn) const;
+  bool uses(Value v) const;
+  void collectValues(std::vector<Value>& out) const;
+  // numeric value for given leaf values; dims are not allowed here
+  int64_t evaluate(const std::function<int64_t(Value)>& valueOf) const;
+  // true (and the linear form) when no floordiv / mod occurs
+  bool toLinear(IndexExpr* out) const;
+  // text in MLIR's infix spelling, leaves named by `nameOf` (dims print as d<i>)
+  std::string str(const std::function<std::string(Value)>& nameOf) const;
+
+  struct Node;
+ private:
+  explicit AffineExpr(std::shared_ptr<const Node> n) : node_(std::move(n)) {}
+  static AffineExpr make(Kind k, int64_t c, const AffineExpr* a, const AffineExpr* b);
+  std::shared_ptr<const Node> node_;
+};
+inline AffineExpr operator*(int64_t c, const AffineExpr& e) { return e * c; }
+inline AffineExpr operator+(int64_t c, const AffineExpr& e) { return e + c; }
+
+// (d0, ..., d{n-1}) -> (results...)
+class AffineMap {
+ public:
+  AffineMap() = default;
+  static AffineMap get(unsigned dimCount, unsigned symbolCount, const std::vector<AffineExpr>& results, Context* ctx = nullptr) {
+    (void)symbolCount;
+    (void)ctx;
+    AffineMap m;
+    m.numDims_ = dimCount;
+    m.results_ = results;
+    return m;
+  }
+  unsigned getNumDims() const { return numDims_; }
+  unsigned getNumResults() const { return static_cast<unsigned>(results_.size()); }
+  const std::vector<AffineExpr>& getResults() const { return results_; }
+  AffineExpr getResult(unsigned i) const { return results_.at(i); }
+  // the results with dim i replaced by operands[i]
+  std::vector<AffineExpr> apply(const std::vector<AffineExpr>& operands) const;
+ private:
+  unsigned numDims_ = 0;
+  std::vector<AffineExpr> results_;
+};
+
 using Attribute = std::variant<int64_t, double, std::string, std::vector<int64_t>>;
 
 enum class OpKind {
   Module, Func, Return, Call, Alloc,
   For, Parallel, Yield, Apply,
   Load, Store, Constant, MulF, AddF, MaxF, DivF, Exp,
-  Barrier, Annotation
+  Barrier, Annotation,
+  VectorLoad, VectorStore,   // affine.vector_load / affine.vector_store: `width` contiguous elements
+  If,                        // affine.if with one condition `cond >= 0`, no else branch
+  IndexConstant              // arith.constant <n> : index
 };
 
 const char* opKindName(OpKind k);
@@ -136,6 +221,13 @@ struct Operation {
   std::vector<int64_t> extents;
   // Load / Store / Apply
   std::vector<IndexExpr> indices;
+  // Load / Store / VectorLoad / VectorStore in general form: one quasi-affine expression per
+  // memref dimension over SSA values (floordiv / mod allowed).  Used instead of `indices` when
+  // not empty.
+  std::vector<AffineExpr> exprs;
+  int64_t width = 1;                      // VectorLoad / VectorStore
+  AffineExpr cond;                        // If: the body runs when cond >= 0
+  int64_t ivalue = 0;                     // IndexConstant
   // Constant
   double fvalue = 0.0;
   // Func
@@ -155,6 +247,11 @@ struct Operation {
   void walk(const std::function<void(Operation*)>& fn);  // pre-order, includes this
   void replaceUsesOfWith(Value from, Value to);          // inside this op (recursively)
   void substituteIndex(Value from, const IndexExpr& to); // inside this op (recursively)
+  void substituteExpr(Value from, const AffineExpr& to); // same with a general expression: ops that use
+                                                         // `from` in a linear index switch to the general form
+  // index expression of memref dimension d, whichever form the op is in
+  AffineExpr indexExpr(size_t d) const;
+  size_t indexRank() const { return exprs.empty() ? indices.size() : exprs.size(); }
   void dump() const;
   void print(std::ostream& os) const;
 };
@@ -235,6 +332,7 @@ class AffineForOp : public OpHandle {
   int64_t getConstantUpperBound() const { return op_->ub; }
   int64_t getStep() const { return op_->step; }
   int64_t tripCount() const { return (op_->ub - op_->lb + op_->step - 1) / op_->step; }
+  bool hasConstantBounds() const { return true; }
   size_t getNumIterOperands() const { return op_->operands.size(); }
   Value getRegionIterArg(size_t i) const { return op_->body->getArgument(1 + i); }
   Value getResult(size_t i = 0) const { return op_->getResult(i); }
@@ -290,6 +388,16 @@ class OpBuilder {
   Value createApply(const IndexExpr& e);
   Value createLoad(Value memref, const std::vector<IndexExpr>& idx);
   Operation* createStore(Value v, Value memref, const std::vector<IndexExpr>& idx);
+  // general-form accesses (see Operation::exprs); width 1 = affine.load / affine.store spelling
+  Value createVectorLoad(Value memref, const std::vector<AffineExpr>& idx, int64_t width);
+  Operation* createVectorStore(Value v, Value memref, const std::vector<AffineExpr>& idx, int64_t width);
+  // affine.if (cond >= 0) { body }
+  Operation* createIf(const AffineExpr& cond);
+  Value createIndexConstant(int64_t v);
+  // user-facing expression builders, spelled as on MLIR's OpBuilder
+  AffineExpr getAffineDimExpr(unsigned position) const { return AffineExpr::dim(position); }
+  AffineExpr getAffineConstantExpr(int64_t c) const { return AffineExpr::constant(c); }
+  std::string getStringAttr(const std::string& s) const { return s; }
   Value createConstant(double v, ScalarKind k);
   Value createBinary(OpKind k, Value a, Value b);
   Value createExp(Value a);
@@ -326,6 +434,10 @@ using ModuleOp = kcgir::ModuleOp;
 using AffineForOp = kcgir::AffineForOp;
 using AffineParallelOp = kcgir::AffineParallelOp;
 using IndexExpr = kcgir::IndexExpr;
+using AffineExpr = kcgir::AffineExpr;
+using AffineMap = kcgir::AffineMap;
+using MemRefType = kcgir::Type;
+template <class Sig> using function_ref = std::function<Sig>;
 namespace func {
 using FuncOp = kcgir::FuncOp;
 using CallOp = kcgir::CallOp;
@@ -338,3 +450,9 @@ using BarrierOp = kcgir::BarrierOp;
 }
 inline bool failed(bool ok) { return !ok; }
 }  // namespace mlir
+
+// Container spellings used by schedules written against the reference's signatures.
+namespace llvm {
+template <class T, unsigned N = 4> using SmallVector = std::vector<T>;
+template <class T> using ArrayRef = std::vector<T>;
+}  // namespace llvm

@@ -1145,6 +1145,18 @@ static void resolve_variant(const kcg_gemm_desc* d, int* bn, bool* pair_mode, lo
   *bn = d->tile_n;
   if (*bn == 0) *bn = (d->precision == KCG_PREC_3XTF32 && small_job) ? 128 : 256;
   *pair_mode = d->cta_group == 2 || (d->cta_group == 0 && d->M > BM && small_job);
+  // Products of at most one wave of 128 x 128 tiles (bf16 / TF32): single CTAs on those tiles put
+  // one tile on every SM at once; wider tiles or CTA pairs leave most SMs idle and lengthen the
+  // one main loop there is (bf16, cold L2: 1024^3 14.3 us against 23.4, 1536^3 17.2 against 26.6,
+  // 512^3 11.0 against 14.2; at 2048^3, two waves, the wider pair tiles win again).  The 3xTF32
+  // path keeps its pairs: there the shared-K split of the few tiles is what fills the SMs.
+  if (d->tile_n == 0 && d->cta_group == 0 && d->precision != KCG_PREC_3XTF32) {
+    const long long t128 = ((d->M + BM - 1) / BM) * ((d->N + 127) / 128) * batch;
+    if (t128 <= 148) {
+      *bn = 128;
+      *pair_mode = false;
+    }
+  }
 }
 
 // The plan itself, for tests: out = {tail tiles, units, share, span, max contributors per tile}.

@@ -126,6 +126,10 @@ const char* opKindName(OpKind k) {
     case OpKind::Exp: return "math.exp";
     case OpKind::Barrier: return "gpu.barrier";
     case OpKind::Annotation: return "kcg.annotation";
+    case OpKind::VectorLoad: return "affine.vector_load";
+    case OpKind::VectorStore: return "affine.vector_store";
+    case OpKind::If: return "affine.if";
+    case OpKind::IndexConstant: return "arith.constant";
   }
   return "?";
 }
@@ -180,13 +184,41 @@ void Operation::replaceUsesOfWith(Value from, Value to) {
       for (auto& t : e.terms) if (t.first == from) t.first = to;
       e.simplify();
     }
+    for (auto& e : op->exprs) e = e.replaceValue(from, AffineExpr::value(to));
+    if (op->kind == OpKind::If) op->cond = op->cond.replaceValue(from, AffineExpr::value(to));
   });
 }
 
 void Operation::substituteIndex(Value from, const IndexExpr& to) {
+  const AffineExpr general = AffineExpr::fromLinear(to);
   walk([&](Operation* op) {
     for (auto& e : op->indices) e.substitute(from, to);
+    for (auto& e : op->exprs) e = e.replaceValue(from, general);
+    if (op->kind == OpKind::If) op->cond = op->cond.replaceValue(from, general);
   });
+}
+
+void Operation::substituteExpr(Value from, const AffineExpr& to) {
+  IndexExpr linear;
+  if (to.toLinear(&linear)) {
+    substituteIndex(from, linear);
+    return;
+  }
+  walk([&](Operation* op) {
+    bool used = false;
+    for (auto& e : op->indices) used = used || e.uses(from);
+    if (used && op->kind != OpKind::Apply) {
+      // the access leaves the linear form
+      for (auto& e : op->indices) op->exprs.push_back(AffineExpr::fromLinear(e));
+      op->indices.clear();
+    }
+    for (auto& e : op->exprs) e = e.replaceValue(from, to);
+    if (op->kind == OpKind::If) op->cond = op->cond.replaceValue(from, to);
+  });
+}
+
+AffineExpr Operation::indexExpr(size_t d) const {
+  return exprs.empty() ? AffineExpr::fromLinear(indices.at(d)) : exprs.at(d);
 }
 
 // ---- Context ------------------------------------------------------------------------------------
@@ -252,6 +284,10 @@ Operation* cloneOp(Operation* src, Context* ctx, std::unordered_map<ValueImpl*, 
     for (auto& t : e.terms) ne.terms.emplace_back(remap(t.first), t.second);
     dst->indices.push_back(std::move(ne));
   }
+  for (auto& e : src->exprs) dst->exprs.push_back(e.mapValues(remap));
+  dst->cond = src->cond.mapValues(remap);
+  dst->width = src->width;
+  dst->ivalue = src->ivalue;
   for (size_t i = 0; i < src->results.size(); ++i) {
     ValueImpl* nv = ctx->newValue(src->results[i]->type, dst, nullptr, static_cast<int>(i));
     vmap[src->results[i]] = nv;
@@ -405,6 +441,39 @@ Operation* OpBuilder::createStore(Value v, Value memref, const std::vector<Index
   return insert(op);
 }
 
+Value OpBuilder::createVectorLoad(Value memref, const std::vector<AffineExpr>& idx, int64_t width) {
+  Operation* op = ctx_->newOp(OpKind::VectorLoad);
+  op->operands = {memref};
+  op->exprs = idx;
+  op->width = width;
+  Value r = addResult(ctx_, op, memref.getType().elementType());
+  insert(op);
+  return r;
+}
+
+Operation* OpBuilder::createVectorStore(Value v, Value memref, const std::vector<AffineExpr>& idx, int64_t width) {
+  Operation* op = ctx_->newOp(OpKind::VectorStore);
+  op->operands = {v, memref};
+  op->exprs = idx;
+  op->width = width;
+  return insert(op);
+}
+
+Operation* OpBuilder::createIf(const AffineExpr& cond) {
+  Operation* op = ctx_->newOp(OpKind::If);
+  op->cond = cond;
+  op->body = ctx_->newBlock(op);
+  return insert(op);
+}
+
+Value OpBuilder::createIndexConstant(int64_t v) {
+  Operation* op = ctx_->newOp(OpKind::IndexConstant);
+  op->ivalue = v;
+  Value r = addResult(ctx_, op, Type::index());
+  insert(op);
+  return r;
+}
+
 Value OpBuilder::createConstant(double v, ScalarKind k) {
   Operation* op = ctx_->newOp(OpKind::Constant);
   op->fvalue = v;
@@ -500,6 +569,15 @@ struct Printer {
     for (size_t i = 0; i < idx.size(); ++i) s += (i ? ", " : "") + expr(idx[i]);
     return s + "]";
   }
+  // index list of an access in either form
+  std::string accessList(const Operation* op) {
+    if (op->exprs.empty()) return indexList(op->indices);
+    std::string s = "[";
+    for (size_t i = 0; i < op->exprs.size(); ++i)
+      s += (i ? ", " : "") + op->exprs[i].str([&](Value v) { return name(v); });
+    return s + "]";
+  }
+  int nextIdxCst = 0;
   static std::string fp(double v) {
     std::ostringstream s;
     s << std::scientific << std::setprecision(6) << v;
@@ -642,12 +720,47 @@ struct Printer {
       }
       case OpKind::Load:
         nameResult(op->results[0], false);
-        os << pad << names[op->results[0]] << " = affine.load " << name(op->operands[0]) << indexList(op->indices)
+        os << pad << names[op->results[0]] << " = affine.load " << name(op->operands[0]) << accessList(op)
            << " : " << op->operands[0].getType().str() << "\n";
         break;
       case OpKind::Store:
         os << pad << "affine.store " << name(op->operands[0]) << ", " << name(op->operands[1])
-           << indexList(op->indices) << " : " << op->operands[1].getType().str() << "\n";
+           << accessList(op) << " : " << op->operands[1].getType().str() << "\n";
+        break;
+      case OpKind::VectorLoad:
+        nameResult(op->results[0], false);
+        os << pad << names[op->results[0]] << " = affine.vector_load " << name(op->operands[0]) << accessList(op) << " : "
+           << op->operands[0].getType().str() << ", vector<" << op->width << "x"
+           << scalarName(op->operands[0].getType().elem) << ">\n";
+        break;
+      case OpKind::VectorStore:
+        os << pad << "affine.vector_store " << name(op->operands[0]) << ", " << name(op->operands[1]) << accessList(op)
+           << " : " << op->operands[1].getType().str() << ", vector<" << op->width << "x"
+           << scalarName(op->operands[1].getType().elem) << ">\n";
+        break;
+      case OpKind::If: {
+        // affine.if affine_set<(d0, ...) : (expr >= 0)>(operands)
+        std::vector<Value> leaves;
+        op->cond.collectValues(leaves);
+        std::vector<Value> uniq;
+        for (auto v : leaves)
+          if (std::find(uniq.begin(), uniq.end(), v) == uniq.end()) uniq.push_back(v);
+        os << pad << "affine.if affine_set<(";
+        for (size_t i = 0; i < uniq.size(); ++i) os << (i ? ", " : "") << "d" << i;
+        os << ") : (" << op->cond.str([&](Value v) {
+          return "d" + std::to_string(std::find(uniq.begin(), uniq.end(), v) - uniq.begin());
+        }) << " >= 0)>(";
+        for (size_t i = 0; i < uniq.size(); ++i) os << (i ? ", " : "") << name(uniq[i]);
+        os << ") {\n";
+        block(op->body, indent + 2);
+        os << pad << "}\n";
+        break;
+      }
+      case OpKind::IndexConstant:
+        names[op->results[0]] = nextIdxCst == 0 ? "%c" + std::to_string(op->ivalue)
+                                                : "%c" + std::to_string(op->ivalue) + "_" + std::to_string(nextIdxCst - 1);
+        ++nextIdxCst;
+        os << pad << names[op->results[0]] << " = arith.constant " << op->ivalue << " : index\n";
         break;
       case OpKind::Constant:
         nameResult(op->results[0], true);
@@ -736,7 +849,26 @@ struct Verifier {
         if (!visible(t.first)) return fail(op, "index operand is not visible");
         if (t.first.getType() != Type::index()) return fail(op, "index operand is not of index type");
       }
+    {
+      std::vector<Value> leaves;
+      for (auto& e : op->exprs) e.collectValues(leaves);
+      if (op->kind == OpKind::If) op->cond.collectValues(leaves);
+      for (auto v : leaves) {
+        if (!visible(v)) return fail(op, "index operand is not visible");
+        if (v.getType() != Type::index()) return fail(op, "index operand is not of index type");
+      }
+    }
     switch (op->kind) {
+      case OpKind::If:
+        return checkBlock(op->body, false);
+      case OpKind::VectorLoad:
+      case OpKind::VectorStore: {
+        const Value mem = op->operands[op->kind == OpKind::VectorLoad ? 0 : 1];
+        if (!mem.getType().isMemRef()) return fail(op, "vector access to a non-memref");
+        if (op->exprs.size() != mem.getType().shape.size()) return fail(op, "rank mismatch");
+        if (op->width < 1) return fail(op, "vector width");
+        return true;
+      }
       case OpKind::For:
         if (op->step <= 0) return fail(op, "non-positive step");
         if (op->operands.size() != op->results.size()) return fail(op, "iter_args / results mismatch");
@@ -756,11 +888,11 @@ struct Verifier {
         return checkBlock(op->body, true);
       case OpKind::Load:
         if (!op->operands[0].getType().isMemRef()) return fail(op, "load from a non-memref");
-        if (op->indices.size() != op->operands[0].getType().shape.size()) return fail(op, "rank mismatch");
+        if (op->indexRank() != op->operands[0].getType().shape.size()) return fail(op, "rank mismatch");
         return true;
       case OpKind::Store:
         if (!op->operands[1].getType().isMemRef()) return fail(op, "store to a non-memref");
-        if (op->indices.size() != op->operands[1].getType().shape.size()) return fail(op, "rank mismatch");
+        if (op->indexRank() != op->operands[1].getType().shape.size()) return fail(op, "rank mismatch");
         if (op->operands[0].getType() != op->operands[1].getType().elementType()) return fail(op, "element type");
         return true;
       case OpKind::Call: {

@@ -301,12 +301,6 @@ void Rewriter::cache_write(mlir::AffineForOp scope, mlir::Value src, mlir::Value
   annotate(scope, Position::begin, "cache_write", {src, cached});
 }
 
-mlir::Operation* Rewriter::vectorize(mlir::AffineForOp readOrWrite, int64_t width) {
-  assert(width == 1 || width == 2 || width == 4 || width == 8);
-  readOrWrite->setAttr("kcg.vectorize", width);
-  return readOrWrite;
-}
-
 mlir::Operation* Rewriter::pipeline(mlir::Value buffer, mlir::AffineForOp compute_at, int64_t stages) {
   assert(stages >= 2);
   mlir::Operation* op = annotate(compute_at, Position::begin, "pipeline", {buffer});
