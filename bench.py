@@ -41,7 +41,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each) of ONE launch of
 # the dominant kernel on a case small enough to capture; scaled to the bench's launch by the tiles
 # (x k-blocks) processed.  None = not captured.
-DRAM_BYTES_GEMM_BF16 = {"shape": (16384, 16384, 16384), "bytes": None}
+DRAM_BYTES_GEMM_BF16 = {"shape": (16384, 16384, 16384), "bytes": 8.8297e9 + 0.5368e9}   # read + written
 DRAM_BYTES_GEMM_BF16_8192 = {"shape": (8192, 8192, 8192), "bytes": 1.141e9}
 DRAM_BYTES_C1 = 60.6e6          # 3xTF32 GEMM 4096x2048x1024 incl. the residual arrays it reads
 
@@ -613,6 +613,51 @@ def run_case(args):
 
 
 # ------------------------------------------------------------------------------------------------
+# the reference's own sweep:  python bench.py --sweep [--sweep-log FILE]
+# ------------------------------------------------------------------------------------------------
+def run_sweep(args):
+    """The demo shape and the 20 square sizes of the reference's harness (test/test.cc:16, 37), in
+    the format of its performance/output.log, with sampled rows of every result held to the CPU
+    nest.  One JSON line per size on stdout; the log text goes to --sweep-log."""
+    import numpy as np
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    from kernelcodegen_b200 import build, harness, ops
+    from oracle import oracle
+
+    build.build()
+    dev = torch.device("cuda:0")
+    log = open(args.sweep_log, "w") if args.sweep_log else sys.stderr
+    shapes = [(4096, 2048, 1024)] + [(s, s, s) for s in harness.SWEEP]
+    for m, n, k in shapes:
+        rec = harness.run_case(m, n, k, check=False, out=log)
+        # parity: the same seeded inputs the harness used, a few rows against the fp32 nest
+        g = torch.Generator(device=dev).manual_seed(m * 31 + n * 17 + k)
+        a = torch.rand((m, k), generator=g, device=dev) * 2 - 1
+        b = torch.rand((k, n), generator=g, device=dev) * 2 - 1
+        c = ops.matmul(a, b)
+        nrows = 8 if k <= 4096 else 3
+        rows = sorted({0, m - 1, *np.random.default_rng(m).integers(0, m, nrows).tolist()})
+        want = oracle.matmul_rows(a[rows].cpu().numpy(), b.cpu().numpy(), list(range(len(rows))))
+        got = c[rows].cpu().numpy()
+        rec["rel_err_vs_cpu_nest"] = float(np.abs(got - want).max() / np.abs(want).max())
+        # the same rows accumulated in float64 tell the two apart: how far the fp32 nest itself and the
+        # kernel are from the exact product
+        exact = oracle.matmul_rows(a[rows].cpu().numpy(), b.cpu().numpy(), list(range(len(rows))), f64=True)
+        rec["rel_err_vs_f64"] = float(np.abs(got - exact).max() / np.abs(exact).max())
+        rec["cpu_nest_vs_f64"] = float(np.abs(want - exact).max() / np.abs(exact).max())
+        rec["rows_checked"] = len(rows)
+        rec["tflops"] = 2.0 * m * n * k / rec["mine_ms"] / 1e9
+        rec["cublas_sgemm_ratio"] = rec["cublas_nn_ms"] / rec["mine_ms"]
+        print(json.dumps(rec), flush=True)
+        del a, b, c
+    if log is not sys.stderr:
+        log.close()
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_ours(args):
@@ -659,13 +704,14 @@ def run_ours(args):
         b[r0:r0 + chunk] = (torch.randn((chunk, N), generator=g, device=dev) * 0.02).bfloat16()
 
     def make_a(r_lo, r_hi):
-        """Rows [r_lo, r_hi) of A: every 128-row block has its own seed, so a rank makes exactly its
-        shard and the bits do not depend on how the rows are dealt out."""
+        """Rows [r_lo, r_hi) of A: every aligned 2048-row chunk has its own seed and is generated whole,
+        so a rank makes only the chunks its shard touches and the bits do not depend on how the rows
+        are dealt out."""
         out = torch.empty((r_hi - r_lo, K), dtype=torch.bfloat16, device=dev)
-        for r0 in range(r_lo - r_lo % 128, r_hi, 128):
+        for r0 in range(r_lo - r_lo % chunk, r_hi, chunk):
             g.manual_seed(40 * 100003 + r0)
-            blk = (torch.randn((128, K), generator=g, device=dev) * 0.02).bfloat16()
-            s0, s1 = max(r0, r_lo), min(r0 + 128, r_hi)
+            blk = (torch.randn((chunk, K), generator=g, device=dev) * 0.02).bfloat16()
+            s0, s1 = max(r0, r_lo), min(r0 + chunk, r_hi)
             out[s0 - r_lo:s1 - r_lo] = blk[s0 - r0:s1 - r0]
         return out
 
@@ -965,7 +1011,12 @@ def main():
                     help="untimed warm-up continues until this many seconds of steps have run (0 = exactly --warmup steps)")
     ap.add_argument("--case", default=None, help="run one small case (for profiler captures) and print its timing")
     ap.add_argument("--iters", type=int, default=3, help="launches of --case")
+    ap.add_argument("--sweep", action="store_true", help="the reference harness's demo shape + 20 square sizes, with parity per size")
+    ap.add_argument("--sweep-log", default=None, help="file for the output.log-format text of --sweep")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.case:
         run_case(args)
         return

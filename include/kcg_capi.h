@@ -292,6 +292,24 @@ kcg_status_t kcg_selftest_wait_timeout(uint32_t iterations);
 /* Test hook: iteration cap of the device-side waits for subsequent launches (0 = default). */
 void kcg_set_spin_limit(uint32_t iterations);
 
+/* Bounds-checking build.  The library can be built a second time with -DKCG_DEBUG_BOUNDS
+ * (libkcg_b200_bounds.so; kernelcodegen_b200.build.build_bounds()).  In that build every global
+ * store of a result and every access to the shared-K scratch is checked against the byte extent
+ * of its buffer, and the launch code checks every tensor-map coordinate it will issue for the
+ * 16-byte rule; a failed device-side check records code 10 in the status word
+ * (kcg_last_device_status) and the offending offset / extent (kcg_debug_bounds_detail), SKIPS the
+ * access and lets the kernel finish: nothing traps and no memory outside the buffers is touched.
+ * It takes the place of a memory sanitizer where none can be run.
+ *   kcg_debug_bounds_enabled     1 in that build, 0 in the normal one;
+ *   kcg_debug_set_extent_limit   test hook: caps the extents the kernels check against (0 = off),
+ *                                so that the reporting path can be exercised on buffers that are in
+ *                                fact large enough (no real out-of-bounds access is ever made);
+ *   kcg_debug_bounds_detail      out2 = {byte offset of the first failed check, extent}.
+ * No counterpart in the reference, whose generated kernels have no bounds checks at all. */
+int kcg_debug_bounds_enabled(void);
+void kcg_debug_set_extent_limit(uint64_t bytes);
+kcg_status_t kcg_debug_bounds_detail(uint64_t* out2);
+
 /* Number of kernel launches this library has issued since load (all threads). */
 uint64_t kcg_launch_count(void);
 

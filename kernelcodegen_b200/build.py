@@ -34,26 +34,37 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def needs_build() -> bool:
-    if not LIB_PATH.exists():
+BOUNDS_LIB_PATH = PKG_DIR / "libkcg_b200_bounds.so"
+
+
+def needs_build(lib: Path = LIB_PATH) -> bool:
+    if not lib.exists():
         return True
-    t = LIB_PATH.stat().st_mtime
+    t = lib.stat().st_mtime
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "kcg_capi.h"]
     return any(p.stat().st_mtime > t for p in deps if p.exists())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build_bounds(force: bool = False) -> Path:
+    """The same sources with -DKCG_DEBUG_BOUNDS (every result store and scratch access checked
+    against its buffer's extent, see include/kcg_capi.h) -> libkcg_b200_bounds.so; selected at load
+    time by KCG_DEBUG_BOUNDS=1 in the environment."""
+    return build(force=force, lib=BOUNDS_LIB_PATH, defines=["-DKCG_DEBUG_BOUNDS"], obj_subdir="build_bounds")
+
+
+def build(force: bool = False, verbose: bool = False, lib: Path = LIB_PATH, defines: list[str] | None = None,
+          obj_subdir: str = "build") -> Path:
     """Compile the library if it is missing or older than its sources."""
-    if not force and not needs_build():
-        return LIB_PATH
+    if not force and not needs_build(lib):
+        return lib
     nvcc = _nvcc()
-    obj_dir = PKG_DIR / "build"
+    obj_dir = PKG_DIR / obj_subdir
     obj_dir.mkdir(exist_ok=True)
     objs = []
     procs = []
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *(defines or []), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -64,14 +75,14 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}")
-    tmp = LIB_PATH.with_suffix(".so.tmp")
+    tmp = lib.with_suffix(".so.tmp")
     link = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
     res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout)
         raise RuntimeError("link failed")
-    os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+    os.replace(tmp, lib)
+    return lib
 
 
 HOST_LIB_PATH = PKG_DIR / "libkcg_runtime.so"
@@ -141,4 +152,5 @@ def compile_program(source: Path, output: Path, extra: list[str] | None = None) 
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_bounds(force="--force" in sys.argv))
     print(build_host(force="--force" in sys.argv))

@@ -10,6 +10,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libkcg_b200.so"
+BOUNDS_LIB_PATH = Path(__file__).resolve().parent / "libkcg_b200_bounds.so"   # -DKCG_DEBUG_BOUNDS build
 
 # enum kcg_status_t
 KCG_OK = 0
@@ -57,6 +58,9 @@ EXPORTED_SYMBOLS = (
     "kcg_peer_wait_status",
     "kcg_last_device_status",
     "kcg_set_spin_limit",
+    "kcg_debug_bounds_enabled",
+    "kcg_debug_set_extent_limit",
+    "kcg_debug_bounds_detail",
     "kcg_selftest_wait_timeout",
     "kcg_launch_count",
     "kcg_status_str",
@@ -105,11 +109,15 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    import os
+
+    # KCG_DEBUG_BOUNDS=1 in the environment selects the bounds-checking build of the same sources
+    path = BOUNDS_LIB_PATH if os.environ.get("KCG_DEBUG_BOUNDS") == "1" else LIB_PATH
+    if not path.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m kernelcodegen_b200.build` "
+            f"{path} is missing: build it with `python -m kernelcodegen_b200.build` "
             "(there is no CPU or PyTorch fallback)")
-    lib = ctypes.CDLL(str(LIB_PATH))
+    lib = ctypes.CDLL(str(path))
     lib.kcg_gemm_workspace_bytes.restype = c_size_t
     lib.kcg_gemm_workspace_bytes.argtypes = [POINTER(GemmDesc)]
     lib.kcg_fmha_workspace_bytes.restype = c_size_t
@@ -166,6 +174,12 @@ def load() -> ctypes.CDLL:
     lib.kcg_selftest_wait_timeout.argtypes = [c_uint32]
     lib.kcg_set_spin_limit.restype = None
     lib.kcg_set_spin_limit.argtypes = [c_uint32]
+    lib.kcg_debug_bounds_enabled.restype = c_int
+    lib.kcg_debug_bounds_enabled.argtypes = []
+    lib.kcg_debug_set_extent_limit.restype = None
+    lib.kcg_debug_set_extent_limit.argtypes = [c_uint64]
+    lib.kcg_debug_bounds_detail.restype = c_int
+    lib.kcg_debug_bounds_detail.argtypes = [POINTER(c_uint64)]
     lib.kcg_launch_count.restype = c_uint64
     lib.kcg_launch_count.argtypes = []
     lib.kcg_status_str.restype = c_char_p

@@ -33,6 +33,39 @@ kcg_status_t device_status_ptr(int** out) {
   return KCG_OK;
 }
 
+// Detail record of the bounds-checking build: {offending byte offset, extent it was checked against}.
+__device__ unsigned long long g_bounds_detail[2];
+std::atomic<unsigned long long> g_extent_limit{0};
+
+kcg_status_t debug_bounds_detail_ptr(unsigned long long** out) {
+#ifdef KCG_DEBUG_BOUNDS
+  static std::mutex mu;
+  static unsigned long long* cache[64] = {};
+  int dev = 0;
+  KCG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return KCG_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    KCG_CUDA_TRY(cudaGetSymbolAddress(&p, g_bounds_detail));
+    KCG_CUDA_TRY(cudaMemset(p, 0, sizeof(unsigned long long) * 2));
+    cache[dev] = static_cast<unsigned long long*>(p);
+  }
+  *out = cache[dev];
+#else
+  *out = nullptr;
+#endif
+  return KCG_OK;
+}
+
+unsigned long long debug_extent_limit() {
+#ifdef KCG_DEBUG_BOUNDS
+  return g_extent_limit.load();
+#else
+  return 0;
+#endif
+}
+
 int device_sm_count() {
   static int cache[64] = {};
   int dev = 0;
@@ -393,6 +426,29 @@ kcg_status_t kcg_selftest_wait_timeout(uint32_t iterations) {
 }
 
 void kcg_set_spin_limit(uint32_t iterations) { g_spin_limit.store(iterations); }
+
+int kcg_debug_bounds_enabled(void) {
+#ifdef KCG_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+void kcg_debug_set_extent_limit(uint64_t bytes) { g_extent_limit.store(bytes); }
+
+kcg_status_t kcg_debug_bounds_detail(uint64_t* out2) {
+  if (!out2) return KCG_BAD_ARGUMENT;
+  out2[0] = out2[1] = 0;
+  unsigned long long* p = nullptr;
+  kcg_status_t st = debug_bounds_detail_ptr(&p);
+  if (st != KCG_OK || !p) return st;
+  unsigned long long v[2] = {0, 0};
+  KCG_CUDA_TRY(cudaMemcpy(v, p, sizeof(v), cudaMemcpyDeviceToHost));
+  out2[0] = v[0];
+  out2[1] = v[1];
+  return KCG_OK;
+}
 
 uint64_t kcg_launch_count(void) { return g_launches.load(); }
 

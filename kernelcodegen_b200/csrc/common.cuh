@@ -18,6 +18,11 @@ extern std::atomic<uint32_t> g_spin_limit;
 // Address of the per-device status word (a __device__ int owned by capi.cu).
 kcg_status_t device_status_ptr(int** out);
 int device_sm_count();
+// Bounds-checking build (KCG_DEBUG_BOUNDS): address of the two-word detail record on the current
+// device, and the test hook that caps the extents the kernels check against (0 = no cap).  In the
+// normal build the pointer stays null and the cap is 0.
+kcg_status_t debug_bounds_detail_ptr(unsigned long long** out);
+unsigned long long debug_extent_limit();
 
 // dims/strides innermost first, strides in bytes for dims 1..rank-1.
 kcg_status_t encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,

@@ -59,6 +59,8 @@ struct FmhaParams {
   int bh_total;      // batch * heads
   int bh_group;      // (batch, head) pairs walked together, see the block-index mapping in the kernel
   int bh_small;      // how many of the groups (the first ones) hold one pair fewer
+  unsigned long long o_extent;          // bounds-checking build: bytes of O
+  unsigned long long* bounds_detail;
 };
 
 template <int D, bool TF>
@@ -482,9 +484,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_before();
       }
     }
-    if (ok && row < p.Sq) {
+    const size_t off = (static_cast<size_t>(bh) * p.Sq + row) * D;
+    if (ok && row < p.Sq &&
+        bounds_ok(off * (p.out_bf16 ? 2 : 4), static_cast<unsigned long long>(D) * (p.out_bf16 ? 2 : 4), p.o_extent,
+                  p.status, p.bounds_detail)) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const size_t off = (static_cast<size_t>(bh) * p.Sq + row) * D;
       if (p.out_bf16) {
         uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.O) + off);
 #pragma unroll
@@ -706,6 +710,10 @@ kcg_status_t fmha_launch_impl(const kcg_fmha_desc* d, const void* Q, const void*
   p.causal = d->causal ? 1 : 0;
   p.out_bf16 = d->dtype_out == KCG_BF16;
   p.scale_log2 = d->scale * 1.4426950408889634f;
+  p.o_extent = static_cast<unsigned long long>(q_elems) * (d->dtype_out == KCG_BF16 ? 2 : 4);
+  if (const unsigned long long cap = debug_extent_limit()) p.o_extent = p.o_extent < cap ? p.o_extent : cap;
+  p.bounds_detail = nullptr;
+  debug_bounds_detail_ptr(&p.bounds_detail);
   kcg_status_t st = device_status_ptr(&p.status);
   if (st != KCG_OK) return st;
   const uint32_t spin = g_spin_limit.load();

@@ -50,6 +50,10 @@ struct GemmParams {
   int relu;
   int* status;
   uint32_t spin;
+  // bounds-checking build: bytes of C (all batch entries) and of the shared-K scratch, and where a
+  // failed check leaves its offset; unused in the normal build
+  unsigned long long c_extent, sk_extent;
+  unsigned long long* bounds_detail;
   // Batched product: `batch` independent M x N x K products; tile index = batch entry major.  The
   // operands are 3-D tensor maps {k, rows, batch}; an operand shared by all entries has batch
   // extent 1 (a_bz / b_bz = 0: its batch coordinate stays 0).  C of entry b starts c_bstride
@@ -238,7 +242,8 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
             for (int dst = 0; dst <= p.n_peers; ++dst) {
               OutT* cp = static_cast<OutT*>(dst == 0 ? p.C : p.peers[dst - 1]) + off;
               for (int i = 0; i < 32; ++i) {
-                if (col + sub * 32 + i < p.N) {
+                if (col + sub * 32 + i < p.N &&
+                    bounds_ok((off + i) * sizeof(OutT), sizeof(OutT), p.c_extent, p.status, p.bounds_detail)) {
                   if (sizeof(OutT) == 2)
                     reinterpret_cast<__nv_bfloat16*>(cp)[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
                   else
@@ -258,7 +263,9 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
             for (int i = 0; i < 8; ++i) {
               const int rloc = i * 4 + rr;
               const int grow = row0 + rloc;
-              if (grow < p.M) {
+              if (grow < p.M &&
+                  bounds_ok((c_off + static_cast<long long>(grow) * p.ldc + col) * sizeof(OutT) + ch * 16, 16, p.c_extent,
+                            p.status, p.bounds_detail)) {
                 const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
                                                                  ((ch ^ (rloc & 7)) << 4));
                 multimem_st_v4(cbase + (c_off + static_cast<long long>(grow) * p.ldc + col) *
@@ -273,7 +280,9 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
             for (int i = 0; i < 8; ++i) {
               const int rloc = i * 4 + rr;
               const int grow = row0 + rloc;
-              if (grow < p.M) {
+              if (grow < p.M &&
+                  bounds_ok((c_off + static_cast<long long>(grow) * p.ldc + col) * sizeof(OutT) + ch * 16, 16, p.c_extent,
+                            p.status, p.bounds_detail)) {
                 const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
                                                                  ((ch ^ (rloc & 7)) << 4));
                 *reinterpret_cast<uint4*>(cbase + (c_off + static_cast<long long>(grow) * p.ldc + col) *
@@ -291,7 +300,11 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
 // c of row `lane` goes to float4 index (c * 8 + j) * 32 + lane: every store instruction of the
 // warp covers 512 contiguous bytes, and the reader uses the same mapping.
 template <int BN>
-__device__ __forceinline__ void write_partial(uint32_t t_row, float* dst, int lane) {
+__device__ __forceinline__ void write_partial(const GemmParams& p, uint32_t t_row, float* dst, int lane) {
+  // the whole 32 x BN slab of this warp must lie inside the scratch the host set aside
+  if (!bounds_ok(reinterpret_cast<const uint8_t*>(dst) - reinterpret_cast<const uint8_t*>(p.sk_partial),
+                 32ull * BN * sizeof(float), p.sk_extent, p.status, p.bounds_detail))
+    return;
   float4* out = reinterpret_cast<float4*>(dst) + lane;
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
@@ -839,7 +852,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int n_contrib = last - first + 1;
         const int slab = (ti * 2 + static_cast<int>(rank)) * 4 + q;
         float* slab_base = p.sk_partial + static_cast<size_t>(slab) * p.sk_maxc * (32 * BN);
-        write_partial<BN>(t_row, slab_base + static_cast<size_t>(pair - first) * (32 * BN), lane);
+        write_partial<BN>(p, t_row, slab_base + static_cast<size_t>(pair - first) * (32 * BN), lane);
         __syncwarp();
         // release the warp's slab and learn how many contributors came before, in one atomic
         int seen = 0;
@@ -1105,6 +1118,7 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
     p.sk_span = pl.span;
     p.sk_maxc = pl.maxc;
     p.sk_partial = static_cast<float*>(sk_ws);
+    p.sk_extent = pl.bytes;
     p.sk_count = counters + (g_sk_row.fetch_add(1) % SK_ROWS) * SK_ROW_INTS;
     pairs = tiles >= max_clusters ? max_clusters : pl.units;
   }
@@ -1404,6 +1418,27 @@ kcg_status_t gemm_batched_launch_impl(const kcg_gemm_desc* d, long long batch, l
     if (st != KCG_OK) return st;
   }
 
+#ifdef KCG_DEBUG_BOUNDS
+  // Every tensor-map coordinate the kernels will issue, checked on the host: the innermost
+  // coordinate times the element size must be a multiple of 16 bytes (nothing checks that before
+  // the copy runs, and a violation loses the context), no coordinate is negative, and the tiles
+  // cover the whole problem.  Coordinates beyond an extent are legal for loads (zero fill).
+  {
+    const long long tm = pair_mode ? 2 * BM : BM;
+    const long long tiles_m = (d->M + tm - 1) / tm, tiles_n = (d->N + bn - 1) / bn, kbs = (d->K + bk - 1) / bk;
+    bool ok = tiles_m * tm >= d->M && tiles_n * bn >= d->N && kbs * bk >= d->K;
+    ok = ok && (static_cast<long long>(bk) * es) % 16 == 0;            // k0 = kb * bk for the K-major operands
+    if (!b_kmajor) {
+      const long long group = 128 / es;                                 // x = n0 + j * group for row-major B
+      ok = ok && (static_cast<long long>(bn) * es) % 16 == 0 && (group * es) % 16 == 0 &&
+           ((pair_mode ? bn / 2 : bn) * static_cast<long long>(es)) % 16 == 0;
+    }
+    if (!ok) {
+      std::fprintf(stderr, "kcg: bounds build: tile / tensor-map coordinate self-check failed\n");
+      return KCG_BAD_ALIGN;
+    }
+  }
+#endif
   GemmParams p;
   p.C = C;
   p.M = static_cast<int>(d->M);
@@ -1414,6 +1449,13 @@ kcg_status_t gemm_batched_launch_impl(const kcg_gemm_desc* d, long long batch, l
   p.a_bz = batch_a > 1 ? 1 : 0;
   p.b_bz = batch_b > 1 ? 1 : 0;
   p.c_bstride = batch > 1 ? stride_c : 0;
+  // extent of C for the bounds-checking build: up to the last element of the last entry's last row
+  p.c_extent = (static_cast<unsigned long long>(batch - 1) * (batch > 1 ? stride_c : 0) +
+                static_cast<unsigned long long>(d->M - 1) * d->ldc + d->N) * os;
+  if (const unsigned long long cap = debug_extent_limit()) p.c_extent = p.c_extent < cap ? p.c_extent : cap;
+  p.sk_extent = 0;
+  p.bounds_detail = nullptr;
+  debug_bounds_detail_ptr(&p.bounds_detail);
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + bn - 1) / bn;
   p.group_m = d->group_m > 0 ? d->group_m : 16;

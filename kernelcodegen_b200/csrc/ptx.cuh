@@ -22,7 +22,30 @@ enum DeviceStatus : int {
   DEV_TIMEOUT_P = 7,          // MMA issuer waited too long for P in shared memory
   DEV_TIMEOUT_Q = 8,          // MMA issuer waited too long for the Q tile
   DEV_TIMEOUT_PEER = 9,       // a rank's completion flag did not arrive in time (kcg_peer_wait_launch)
+  DEV_BOUNDS = 10,            // bounds-checking build: a store or a scratch access fell outside its buffer
 };
+
+// Bounds-checking build (-DKCG_DEBUG_BOUNDS; the sanitizer tools are not available everywhere): every
+// global store of a result and every scratch access is preceded by a check of its byte range against
+// the extent the host computed for that buffer.  An access that fails records DEV_BOUNDS in the status
+// word and the offending byte offset in `detail`, and is SKIPPED -- the kernel never touches memory
+// outside the buffers it was given, and it never traps.  In the normal build the check is `true`.
+#ifdef KCG_DEBUG_BOUNDS
+__device__ __forceinline__ bool bounds_ok(unsigned long long offset_bytes, unsigned long long bytes,
+                                          unsigned long long extent_bytes, int* status, unsigned long long* detail) {
+  if (extent_bytes == 0 || offset_bytes + bytes <= extent_bytes) return true;
+  if (status && atomicCAS(status, 0, static_cast<int>(DEV_BOUNDS)) == 0 && detail) {
+    detail[0] = offset_bytes;
+    detail[1] = extent_bytes;
+  }
+  return false;
+}
+#else
+__device__ __forceinline__ bool bounds_ok(unsigned long long, unsigned long long, unsigned long long, int*,
+                                          unsigned long long*) {
+  return true;
+}
+#endif
 
 #ifndef KCG_SPIN_LIMIT
 #define KCG_SPIN_LIMIT (1u << 24)

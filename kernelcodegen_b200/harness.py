@@ -48,6 +48,22 @@ def _time(fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
+def _cta_threads(m: int, n: int, k: int) -> int:
+    """Threads per CTA of the launch the library chooses for this fp32 product."""
+    import ctypes
+
+    from . import capi
+
+    d = capi.GemmDesc()
+    d.M, d.N, d.K = m, n, k
+    d.lda, d.ldb, d.ldc = k, n, n
+    d.dtype_in = d.dtype_out = capi.KCG_F32
+    d.precision = capi.KCG_PREC_3XTF32
+    geo = (ctypes.c_int32 * 6)()
+    capi.check(capi.load().kcg_gemm_launch_geometry(ctypes.byref(d), geo), "kcg_gemm_launch_geometry")
+    return int(geo[1])
+
+
 def run_case(m: int, n: int, k: int, check: bool, out=sys.stdout) -> dict:
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev).manual_seed(m * 31 + n * 17 + k)
@@ -63,13 +79,18 @@ def run_case(m: int, n: int, k: int, check: bool, out=sys.stdout) -> dict:
     at, bt = a.t().contiguous(), b.t().contiguous()
     ct = torch.empty((n, m), device=dev)
     tt = _time(lambda: torch.matmul(bt, at, out=ct), iters)   # (A.B)^T = B^T.A^T: both operands transposed
+    torch.backends.cuda.matmul.allow_tf32 = True
+    tf32 = _time(lambda: torch.matmul(a, b, out=ref), iters)    # the library's one-pass TF32 product, for scale
+    torch.backends.cuda.matmul.allow_tf32 = False
     err = None
     if check:
         err = ((c.double() - a.double() @ b.double()).abs().max() / (a.double() @ b.double()).abs().max()).item()
     torch.backends.cuda.matmul.allow_tf32 = old
     print("Matrix size : ", file=out)
     print(f" --- M --- : {m}\n --- N --- : {n}\n --- K --- : {k}\n", file=out)
-    print("Occupancy: 9.4% (one 192-thread CTA per SM; the work is done by TMA and the tensor core)", file=out)
+    threads = _cta_threads(m, n, k)
+    print(f"Occupancy: {100.0 * threads / 2048:.1f}% (one {threads}-thread CTA per SM; the work is done by TMA and the tensor core)",
+          file=out)
     print(f"My Matmul Latency = {mine:.6g} ms\n", file=out)
     print(f"cublas Latency(NN) = {nn:.6g} ms", file=out)
     print(f"cublas Ratio(NN) = {100.0 * nn / mine:.6g}%\n", file=out)
@@ -77,7 +98,8 @@ def run_case(m: int, n: int, k: int, check: bool, out=sys.stdout) -> dict:
     print(f"cublas Ratio(TT) = {100.0 * tt / mine:.6g}%\n", file=out)
     if err is not None:
         print(f"max relative error vs fp64 = {err:.3e}", file=out)
-    return {"m": m, "n": n, "k": k, "mine_ms": mine, "cublas_nn_ms": nn, "cublas_tt_ms": tt, "rel_err": err}
+    return {"m": m, "n": n, "k": k, "mine_ms": mine, "cublas_nn_ms": nn, "cublas_tt_ms": tt, "cublas_tf32_ms": tf32,
+            "rel_err": err}
 
 
 def parse_log(text: str):
