@@ -48,6 +48,10 @@ struct GemmParams {
   long long ldc;
   int tiles_m, tiles_n, group_m;
   int relu;
+  // Long-K fp32 products run as several launches over K ranges (see gemm_batched_launch_impl): a
+  // launch with `accum` adds its tile to what C already holds (fp32, round-to-nearest, in the
+  // epilogue's write loop) and applies ReLU afterwards when `relu_late` is set.
+  int accum, relu_late;
   int* status;
   uint32_t spin;
   // bounds-checking build: bytes of C (all batch entries) and of the shared-K scratch, and where a
@@ -244,10 +248,15 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
               for (int i = 0; i < 32; ++i) {
                 if (col + sub * 32 + i < p.N &&
                     bounds_ok((off + i) * sizeof(OutT), sizeof(OutT), p.c_extent, p.status, p.bounds_detail)) {
-                  if (sizeof(OutT) == 2)
+                  if (sizeof(OutT) == 2) {
                     reinterpret_cast<__nv_bfloat16*>(cp)[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
-                  else
+                  } else if (p.accum) {
+                    float v = reinterpret_cast<float*>(cp)[i] + __uint_as_float(r[i]);
+                    if (p.relu_late) v = v > 0.f ? v : 0.f;
+                    reinterpret_cast<float*>(cp)[i] = v;
+                  } else {
                     reinterpret_cast<uint32_t*>(cp)[i] = r[i];
+                  }
                 }
               }
             }
@@ -283,11 +292,24 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t t_row, 
               if (grow < p.M &&
                   bounds_ok((c_off + static_cast<long long>(grow) * p.ldc + col) * sizeof(OutT) + ch * 16, 16, p.c_extent,
                             p.status, p.bounds_detail)) {
-                const uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
-                                                                 ((ch ^ (rloc & 7)) << 4));
-                *reinterpret_cast<uint4*>(cbase + (c_off + static_cast<long long>(grow) * p.ldc + col) *
-                                                      static_cast<long long>(sizeof(OutT)) +
-                                          ch * 16) = v;
+                uint4 v = *reinterpret_cast<const uint4*>(epi_stage + rloc * 128 +
+                                                           ((ch ^ (rloc & 7)) << 4));
+                uint4* out = reinterpret_cast<uint4*>(cbase + (c_off + static_cast<long long>(grow) * p.ldc + col) *
+                                                                  static_cast<long long>(sizeof(OutT)) +
+                                                      ch * 16);
+                if (sizeof(OutT) == 4 && p.accum) {
+                  const uint4 old = *out;
+                  float4 f = make_float4(__uint_as_float(old.x) + __uint_as_float(v.x), __uint_as_float(old.y) + __uint_as_float(v.y),
+                                         __uint_as_float(old.z) + __uint_as_float(v.z), __uint_as_float(old.w) + __uint_as_float(v.w));
+                  if (p.relu_late) {
+                    f.x = f.x > 0.f ? f.x : 0.f;
+                    f.y = f.y > 0.f ? f.y : 0.f;
+                    f.z = f.z > 0.f ? f.z : 0.f;
+                    f.w = f.w > 0.f ? f.w : 0.f;
+                  }
+                  v = make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
+                }
+                *out = v;
               }
             }
           }
@@ -1052,7 +1074,9 @@ kcg_status_t launch_instance(const CUtensorMap& tA, const CUtensorMap& tB, const
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cfg.attrs = attr;
-  cfg.numAttrs = (KIND == 2) ? 1 : 0;   // 3xTF32: overlap the set-up with the residual pass before it
+  // 3xTF32: overlap the set-up with the residual pass before it (not for a launch that adds to
+  // the C the launch before it wrote)
+  cfg.numAttrs = (KIND == 2 && !p.accum) ? 1 : 0;
   KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p));
   g_launches.fetch_add(1);
   return KCG_OK;
@@ -1123,7 +1147,7 @@ kcg_status_t launch_pair_instance(const CUtensorMap& tA, const CUtensorMap& tB, 
     pairs = tiles >= max_clusters ? max_clusters : pl.units;
   }
   cfg.gridDim = dim3(2 * pairs);
-  cfg.numAttrs = (KIND == 2) ? 2 : 1;   // 3xTF32: overlap the set-up with the residual pass before it
+  cfg.numAttrs = (KIND == 2 && !p.accum) ? 2 : 1;   // 3xTF32: overlap the set-up with the residual pass before it
   KCG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tA, tB, tA2, tB2, p));
   g_launches.fetch_add(1);
   return KCG_OK;
@@ -1376,133 +1400,158 @@ kcg_status_t gemm_batched_launch_impl(const kcg_gemm_desc* d, long long batch, l
   if (batch_a == 1) sa_elems = sa2_elems = d->M * lda;
   if (batch_b == 1) sb_elems = sb2_elems = (b_kmajor ? d->N : d->K) * ldb;
 
-  using Cfg0 = GemmCfg<0, 128>;
-  (void)sizeof(Cfg0);
-  const CUtensorMapDataType dt =
-      kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  const uint32_t bk = 128 / es;
-  CUtensorMap tA, tB, tA2, tB2;
-  {
-    const uint64_t dims[3] = {static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->M), static_cast<uint64_t>(batch_a)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(lda) * es, static_cast<uint64_t>(sa_elems) * es};
-    const uint64_t strides2[2] = {static_cast<uint64_t>(lda2) * es, static_cast<uint64_t>(sa2_elems) * es};
-    const uint32_t box[3] = {bk, BM, 1};
-    kcg_status_t st = encode_tmap(&tA, dt, 3, pa, dims, strides, box);
-    if (st != KCG_OK) return st;
-    st = encode_tmap(&tA2, dt, 3, pa2, dims, strides2, box);
-    if (st != KCG_OK) return st;
-  }
-  {
-    uint64_t dims[3];
-    uint32_t box[3];
-    dims[2] = static_cast<uint64_t>(batch_b);
-    box[2] = 1;
-    if (b_kmajor) {  // B stored [N, K]
-      dims[0] = d->K;
-      dims[1] = d->N;
-      box[0] = bk;
-      box[1] = pair_mode ? bn / 2 : bn;
-    } else {  // B stored [K, N]
-      dims[0] = d->N;
-      dims[1] = d->K;
-      box[0] = 128 / es;
-      box[1] = bk;
+  // One launch over the K range [k0, k0 + kc): the tensor maps start k0 elements into the operands.
+  auto launch_range = [&](long long k0, long long kc, int accum, bool relu_now, bool relu_late) -> kcg_status_t {
+    using Cfg0 = GemmCfg<0, 128>;
+    (void)sizeof(Cfg0);
+    const CUtensorMapDataType dt =
+        kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const uint32_t bk = 128 / es;
+    CUtensorMap tA, tB, tA2, tB2;
+    {
+      const uint64_t dims[3] = {static_cast<uint64_t>(kc), static_cast<uint64_t>(d->M), static_cast<uint64_t>(batch_a)};
+      const uint64_t strides[2] = {static_cast<uint64_t>(lda) * es, static_cast<uint64_t>(sa_elems) * es};
+      const uint64_t strides2[2] = {static_cast<uint64_t>(lda2) * es, static_cast<uint64_t>(sa2_elems) * es};
+      const uint32_t box[3] = {bk, BM, 1};
+      kcg_status_t st = encode_tmap(&tA, dt, 3, static_cast<const uint8_t*>(pa) + k0 * es, dims, strides, box);
+      if (st != KCG_OK) return st;
+      st = encode_tmap(&tA2, dt, 3, static_cast<const uint8_t*>(pa2) + k0 * es, dims, strides2, box);
+      if (st != KCG_OK) return st;
     }
-    const uint64_t strides[2] = {static_cast<uint64_t>(ldb) * es, static_cast<uint64_t>(sb_elems) * es};
-    const CUtensorMapSwizzle sw = (!b_kmajor && es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                                                         : CU_TENSOR_MAP_SWIZZLE_128B;
-    const uint64_t strides2[2] = {static_cast<uint64_t>(ldb2) * es, static_cast<uint64_t>(sb2_elems) * es};
-    kcg_status_t st = encode_tmap(&tB, dt, 3, pb, dims, strides, box, sw);
-    if (st != KCG_OK) return st;
-    st = encode_tmap(&tB2, dt, 3, pb2, dims, strides2, box, sw);
-    if (st != KCG_OK) return st;
-  }
+    {
+      uint64_t dims[3];
+      uint32_t box[3];
+      dims[2] = static_cast<uint64_t>(batch_b);
+      box[2] = 1;
+      if (b_kmajor) {  // B stored [N, K]
+        dims[0] = static_cast<uint64_t>(kc);
+        dims[1] = d->N;
+        box[0] = bk;
+        box[1] = pair_mode ? bn / 2 : bn;
+      } else {  // B stored [K, N]
+        dims[0] = d->N;
+        dims[1] = static_cast<uint64_t>(kc);
+        box[0] = 128 / es;
+        box[1] = bk;
+      }
+      const uint64_t strides[2] = {static_cast<uint64_t>(ldb) * es, static_cast<uint64_t>(sb_elems) * es};
+      const CUtensorMapSwizzle sw = (!b_kmajor && es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                           : CU_TENSOR_MAP_SWIZZLE_128B;
+      const uint64_t strides2[2] = {static_cast<uint64_t>(ldb2) * es, static_cast<uint64_t>(sb2_elems) * es};
+      kcg_status_t st = encode_tmap(&tB, dt, 3, static_cast<const uint8_t*>(pb) + (b_kmajor ? k0 : k0 * ldb) * es, dims, strides, box, sw);
+      if (st != KCG_OK) return st;
+      st = encode_tmap(&tB2, dt, 3, static_cast<const uint8_t*>(pb2) + (b_kmajor ? k0 : k0 * ldb2) * es, dims, strides2, box, sw);
+      if (st != KCG_OK) return st;
+    }
 
-#ifdef KCG_DEBUG_BOUNDS
-  // Every tensor-map coordinate the kernels will issue, checked on the host: the innermost
-  // coordinate times the element size must be a multiple of 16 bytes (nothing checks that before
-  // the copy runs, and a violation loses the context), no coordinate is negative, and the tiles
-  // cover the whole problem.  Coordinates beyond an extent are legal for loads (zero fill).
-  {
-    const long long tm = pair_mode ? 2 * BM : BM;
-    const long long tiles_m = (d->M + tm - 1) / tm, tiles_n = (d->N + bn - 1) / bn, kbs = (d->K + bk - 1) / bk;
-    bool ok = tiles_m * tm >= d->M && tiles_n * bn >= d->N && kbs * bk >= d->K;
-    ok = ok && (static_cast<long long>(bk) * es) % 16 == 0;            // k0 = kb * bk for the K-major operands
-    if (!b_kmajor) {
-      const long long group = 128 / es;                                 // x = n0 + j * group for row-major B
-      ok = ok && (static_cast<long long>(bn) * es) % 16 == 0 && (group * es) % 16 == 0 &&
-           ((pair_mode ? bn / 2 : bn) * static_cast<long long>(es)) % 16 == 0;
+  #ifdef KCG_DEBUG_BOUNDS
+    // Every tensor-map coordinate the kernels will issue, checked on the host: the innermost
+    // coordinate times the element size must be a multiple of 16 bytes (nothing checks that before
+    // the copy runs, and a violation loses the context), no coordinate is negative, and the tiles
+    // cover the whole problem.  Coordinates beyond an extent are legal for loads (zero fill).
+    {
+      const long long tm = pair_mode ? 2 * BM : BM;
+      const long long tiles_m = (d->M + tm - 1) / tm, tiles_n = (d->N + bn - 1) / bn, kbs = (kc + bk - 1) / bk;
+      bool ok = tiles_m * tm >= d->M && tiles_n * bn >= d->N && kbs * bk >= kc;
+      ok = ok && (static_cast<long long>(bk) * es) % 16 == 0;            // k0 = kb * bk for the K-major operands
+      if (!b_kmajor) {
+        const long long group = 128 / es;                                 // x = n0 + j * group for row-major B
+        ok = ok && (static_cast<long long>(bn) * es) % 16 == 0 && (group * es) % 16 == 0 &&
+             ((pair_mode ? bn / 2 : bn) * static_cast<long long>(es)) % 16 == 0;
+      }
+      if (!ok) {
+        std::fprintf(stderr, "kcg: bounds build: tile / tensor-map coordinate self-check failed\n");
+        return KCG_BAD_ALIGN;
+      }
     }
-    if (!ok) {
-      std::fprintf(stderr, "kcg: bounds build: tile / tensor-map coordinate self-check failed\n");
-      return KCG_BAD_ALIGN;
-    }
-  }
-#endif
-  GemmParams p;
-  p.C = C;
-  p.M = static_cast<int>(d->M);
-  p.N = static_cast<int>(d->N);
-  p.K = static_cast<int>(d->K);
-  p.ldc = d->ldc;
-  p.batch = static_cast<int>(batch);
-  p.a_bz = batch_a > 1 ? 1 : 0;
-  p.b_bz = batch_b > 1 ? 1 : 0;
-  p.c_bstride = batch > 1 ? stride_c : 0;
-  // extent of C for the bounds-checking build: up to the last element of the last entry's last row
-  p.c_extent = (static_cast<unsigned long long>(batch - 1) * (batch > 1 ? stride_c : 0) +
-                static_cast<unsigned long long>(d->M - 1) * d->ldc + d->N) * os;
-  if (const unsigned long long cap = debug_extent_limit()) p.c_extent = p.c_extent < cap ? p.c_extent : cap;
-  p.sk_extent = 0;
-  p.bounds_detail = nullptr;
-  debug_bounds_detail_ptr(&p.bounds_detail);
-  p.tiles_m = (p.M + BM - 1) / BM;
-  p.tiles_n = (p.N + bn - 1) / bn;
-  p.group_m = d->group_m > 0 ? d->group_m : 16;
-  p.relu = d->epilogue == KCG_EPI_RELU;
-  kcg_status_t st = device_status_ptr(&p.status);
-  if (st != KCG_OK) return st;
-  const uint32_t spin = g_spin_limit.load();
-  p.spin = spin ? spin : KCG_SPIN_LIMIT;
-  p.n_peers = d->n_peers;
-  for (int i = 0; i < 8; ++i) p.peers[i] = i < d->n_peers ? d->peer_c[i] : nullptr;
-  p.mc = d->mc_c;
-  p.n_flags = d->n_done_flags;
-  p.flag_value = d->done_value;
-  for (int i = 0; i < 9; ++i) p.flags[i] = i < d->n_done_flags ? static_cast<uint32_t*>(d->done_flags[i]) : nullptr;
-  p.done_counter = nullptr;
-  if (p.n_flags > 0) {
-    int* counters = nullptr;
-    st = done_counters_ptr(&counters);
+  #endif
+    GemmParams p;
+    p.C = C;
+    p.M = static_cast<int>(d->M);
+    p.N = static_cast<int>(d->N);
+    p.K = static_cast<int>(kc);
+    p.ldc = d->ldc;
+    p.batch = static_cast<int>(batch);
+    p.a_bz = batch_a > 1 ? 1 : 0;
+    p.b_bz = batch_b > 1 ? 1 : 0;
+    p.c_bstride = batch > 1 ? stride_c : 0;
+    // extent of C for the bounds-checking build: up to the last element of the last entry's last row
+    p.c_extent = (static_cast<unsigned long long>(batch - 1) * (batch > 1 ? stride_c : 0) +
+                  static_cast<unsigned long long>(d->M - 1) * d->ldc + d->N) * os;
+    if (const unsigned long long cap = debug_extent_limit()) p.c_extent = p.c_extent < cap ? p.c_extent : cap;
+    p.sk_extent = 0;
+    p.bounds_detail = nullptr;
+    debug_bounds_detail_ptr(&p.bounds_detail);
+    p.tiles_m = (p.M + BM - 1) / BM;
+    p.tiles_n = (p.N + bn - 1) / bn;
+    p.group_m = d->group_m > 0 ? d->group_m : 16;
+    p.relu = relu_now ? 1 : 0;
+    p.accum = accum;
+    p.relu_late = relu_late ? 1 : 0;
+    kcg_status_t st = device_status_ptr(&p.status);
     if (st != KCG_OK) return st;
-    p.done_counter = counters + (g_done_row.fetch_add(1) % DONE_ROWS) * DONE_STRIDE;
-  }
-  p.sk_tiles = p.sk_units = p.sk_share = p.sk_span = p.sk_maxc = 0;
-  p.sk_partial = nullptr;
-  p.sk_count = nullptr;
+    const uint32_t spin = g_spin_limit.load();
+    p.spin = spin ? spin : KCG_SPIN_LIMIT;
+    p.n_peers = d->n_peers;
+    for (int i = 0; i < 8; ++i) p.peers[i] = i < d->n_peers ? d->peer_c[i] : nullptr;
+    p.mc = d->mc_c;
+    p.n_flags = d->n_done_flags;
+    p.flag_value = d->done_value;
+    for (int i = 0; i < 9; ++i) p.flags[i] = i < d->n_done_flags ? static_cast<uint32_t*>(d->done_flags[i]) : nullptr;
+    p.done_counter = nullptr;
+    if (p.n_flags > 0) {
+      int* counters = nullptr;
+      st = done_counters_ptr(&counters);
+      if (st != KCG_OK) return st;
+      p.done_counter = counters + (g_done_row.fetch_add(1) % DONE_ROWS) * DONE_STRIDE;
+    }
+    p.sk_tiles = p.sk_units = p.sk_share = p.sk_span = p.sk_maxc = 0;
+    p.sk_partial = nullptr;
+    p.sk_count = nullptr;
 
-  if (pair_mode) {
-    // what follows the residual arrays in the workspace is free for the shared-K tail
-    void* sk_ws = (ws && aligned16(ws) && ws_bytes > lo_bytes) ? static_cast<uint8_t*>(ws) + lo_bytes : nullptr;
-    const size_t sk_bytes = sk_ws ? ws_bytes - lo_bytes : 0;
+    if (pair_mode) {
+      // what follows the residual arrays in the workspace is free for the shared-K tail
+      void* sk_ws = (ws && aligned16(ws) && ws_bytes > lo_bytes) ? static_cast<uint8_t*>(ws) + lo_bytes : nullptr;
+      const size_t sk_bytes = sk_ws ? ws_bytes - lo_bytes : 0;
+      if (kind == 0) {
+        if (d->dtype_out == KCG_BF16)
+          return dispatch_pair_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws,
+                                                       sk_bytes);
+        return dispatch_pair_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
+      }
+      if (kind == 1)
+        return dispatch_pair_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
+      return dispatch_pair_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
+    }
     if (kind == 0) {
       if (d->dtype_out == KCG_BF16)
-        return dispatch_pair_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws,
-                                                     sk_bytes);
-      return dispatch_pair_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
+        return dispatch_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages,
+                                                stream);
+      return dispatch_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
     }
-    if (kind == 1)
-      return dispatch_pair_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
-    return dispatch_pair_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream, sk_ws, sk_bytes);
+    if (kind == 1) return dispatch_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+    return dispatch_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+  };
+
+  // The tensor core adds into its fp32 accumulator with truncation, so the 3xTF32 result drifts from
+  // the exact product in proportion to K (about 1.8e-5 of max|C| per 2048 of K with uniform inputs)
+  // and would leave the 1e-4 contract near K = 12000.  Longer products are therefore run as
+  // several launches over K ranges of 4096; each launch after the first adds its tile to C in the
+  // epilogue with round-to-nearest fp32 adds (ReLU on the last one), which resets the drift per
+  // range.  Costs one extra read and write of C per range.
+  constexpr long long K_RANGE = 4096, K_WHOLE = 8192;
+  const bool relu = d->epilogue == KCG_EPI_RELU;
+  if (kind == 2 && batch == 1 && d->K > K_WHOLE && d->n_peers == 0 && !d->mc_c && d->n_done_flags == 0) {
+    const long long ranges = (d->K + K_RANGE - 1) / K_RANGE;
+    for (long long r = 0; r < ranges; ++r) {
+      const long long k0 = r * K_RANGE, kc = std::min<long long>(K_RANGE, d->K - k0);
+      const bool last = r + 1 == ranges;
+      const kcg_status_t st = launch_range(k0, kc, r > 0 ? 1 : 0, false, last && relu && r > 0);
+      if (st != KCG_OK) return st;
+    }
+    return KCG_OK;
   }
-  if (kind == 0) {
-    if (d->dtype_out == KCG_BF16)
-      return dispatch_shape<0, __nv_bfloat16>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages,
-                                              stream);
-    return dispatch_shape<0, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
-  }
-  if (kind == 1) return dispatch_shape<1, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
-  return dispatch_shape<2, float>(bn, b_kmajor, tA, tB, tA2, tB2, p, d->stages, stream);
+  return launch_range(0, d->K, 0, relu, false);
 }
 
 kcg_status_t gemm_launch_impl(const kcg_gemm_desc* d, const void* A, const void* B, void* C,

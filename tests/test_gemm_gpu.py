@@ -156,6 +156,28 @@ def test_config_large_bf16_matmul_relu(cuda_device, size):
     assert ops.last_device_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k,b_col_major", [(128, 256, 16384, False), (200, 136, 9000, True), (256, 128, 12288, False)])
+def test_fp32_contract_holds_for_long_k(cuda_device, m, n, k, b_col_major):
+    """Products with K > 8192 run as several launches over K ranges that add into C with
+    round-to-nearest fp32 adds: the tensor core's truncating accumulator would otherwise drift
+    past the 1e-4 contract near K = 12000 (1.45e-4 at 16384 in one launch)."""
+    from kernelcodegen_b200 import ops
+
+    a = uniform((m, k), 70)
+    b = uniform((n, k) if b_col_major else (k, n), 71)
+    bb = b.t().contiguous() if b_col_major else b
+    rows = list(range(0, m, max(1, m // 16)))
+    want = np.maximum(oracle.matmul_rows(a.numpy(), bb.numpy(), rows), 0.0)
+    exact = np.maximum(oracle.matmul_rows(a.numpy(), bb.numpy(), rows, f64=True), 0.0)
+    before = ops.launch_count()
+    c = ops.matmul_relu(a.to(cuda_device), b.to(cuda_device), b_col_major=b_col_major)
+    assert ops.launch_count() - before == 1 + (k + 4095) // 4096      # residual pass + one launch per K range
+    got = c.cpu().numpy()[rows]
+    assert rel_err(got, want) <= FP32_TOL
+    assert rel_err(got, exact) <= 5e-5
+    assert (c >= 0).all() and ops.last_device_status() == 0
+
+
 def test_strided_operands_and_out(cuda_device):
     from kernelcodegen_b200 import ops
 
