@@ -822,6 +822,18 @@ def run_ours(args):
                            "bar": 2e-2, "peer_block_equals_local_recomputation_256_rows": bool(t[1].item() == 0.0)}
         del a_peer, mine
 
+    # which kernel the library runs for this rank's block, from its own geometry query
+    import ctypes
+
+    gd = capi.GemmDesc()
+    gd.M, gd.N, gd.K = rows, N, K
+    gd.lda, gd.ldb, gd.ldc = K, N, N
+    gd.dtype_in = gd.dtype_out = capi.KCG_BF16
+    gd.precision = capi.KCG_PREC_BF16
+    geo = (ctypes.c_int32 * 6)()
+    lib.kcg_gemm_launch_geometry(ctypes.byref(gd), geo)
+    kernel_name = (f"{'gemm_pair_kernel' if geo[2] == 2 else 'gemm_kernel'}<bf16, tile {geo[3]}x{geo[4]}x64> (tcgen05/TMEM), "
+                   f"grid {geo[0]} x {geo[1]} threads, {geo[5]} tiles, one launch per step per GPU")
     peak_sust = peaks["bf16_tflops_sustained"]
     per_gpu = value / world
     if DRAM_BYTES_GEMM_BF16["bytes"] is not None:
@@ -834,7 +846,7 @@ def run_ours(args):
     roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak_sust, "unit": "TFLOP/s",
                 "frac": per_gpu / peak_sust, "traffic": traffic, "algorithmic_bytes": algo_bytes,
                 "traffic_def": f"ncu dram bytes of one {sm_}^3 launch x tiles x k-blocks of this launch",
-                "kernel": "gemm_kernel<bf16, 128x256x64, 4 stages> (tcgen05/TMEM), one launch per step per GPU",
+                "kernel": kernel_name,
                 "peak_def": f"cuBLAS bf16 sustained, {peak_src} (burst {peaks['bf16_tflops']:.0f}: frac {per_gpu / peaks['bf16_tflops']:.3f})",
                 "per_gpu": True, "flop_per_launch": 2.0 * rows * N * K,
                 "from": "the timed steps (value / n_gpus)"}
