@@ -78,14 +78,32 @@ struct FmhaCfg {
 
 // Register re-balancing.  The CTA is launched with 384 threads x 168 registers = 64512; the
 // pool never grows, so after the change the three warpgroups must still fit in 64512:
-// 128 x 56 + 256 x 224 = 64512 exactly.  (setmaxnreg.inc waits, unbounded, for registers to be
-// released -- a budget that does not add up hangs the CTA.)
-static_assert(128 * 56 + 256 * 224 <= 384 * 168, "setmaxnreg budget must fit the launch allocation");
-__device__ __forceinline__ void reg_dealloc_56() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
+// 128 x 96 + 256 x 200 = 63488.  (The producer / issuer warps spill below 96 registers -- at 56
+// they cost 8 % -- and the softmax warps need fewer than 190.  setmaxnreg.inc waits, unbounded,
+// for registers to be released: a budget that does not add up hangs the CTA.)
+static_assert(128 * 96 + 256 * 200 <= 384 * 168, "setmaxnreg budget must fit the launch allocation");
+__device__ __forceinline__ void reg_dealloc_96() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 96;" ::: "memory");
 }
-__device__ __forceinline__ void reg_alloc_224() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+__device__ __forceinline__ void reg_alloc_200() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 200;" ::: "memory");
+}
+
+// 2^x of a pair; POLY eighths of the pairs (a fixed pattern over the pair index, so that the two
+// kinds of instruction interleave) take it from the FMA-pipe cubic, the rest from the MUFU unit.
+// Measured: with head dimension 64 in bf16 the tensor core needs half as long per block as the
+// MUFU unit and a share of 3/8 gains 9 %; with head dimension 128, or TF32 operands, the two
+// are level and any share costs 1-9 %.
+template <int POLY>
+__device__ __forceinline__ float2 exp2_pair(int g, int pi, float2 x) {
+  if (((pi * 5 + g * 3) & 7) < POLY) {
+    x.x = fmaxf(x.x, -125.f);   // masked keys (-inf) and far tails end as 2^-125, nothing in the sums
+    x.y = fmaxf(x.y, -125.f);
+    return ex2_poly2(x);
+  }
+  x.x = ex2_approx(x.x);
+  x.y = ex2_approx(x.y);
+  return x;
 }
 
 template <int D, bool TF>
@@ -98,6 +116,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int DPANELS = Cfg::DPANELS;
   constexpr int PW = Cfg::PANEL_ELEMS;
   constexpr int UK = Cfg::UMMA_K;
+  constexpr int POLY = (!TF && D == 64) ? 3 : 0;     // eighths of the exponentials on the FMA pipe
   constexpr uint32_t FMT = TF ? UMMA_FMT_TF32 : UMMA_FMT_BF16;
   constexpr uint32_t IDESC_S = make_idesc(FMT, BQ, BKV, 0, 0);
   constexpr uint32_t IDESC_PV = make_idesc(FMT, BQ, D, 0, 1);
@@ -208,7 +227,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-    reg_dealloc_56();
+    reg_dealloc_96();
     if (warp == 0 && lane == 0 && n_kv > 0) {
       // ------------------------------- TMA producer -----------------------------------------
       // (block 0 and the Q tiles were issued before the CTA-wide synchronisation above)
@@ -345,7 +364,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------- softmax / output (2 x 4 warps) --------------------------
-    reg_alloc_224();
+    reg_alloc_200();
     const int t = (warp >> 2) - 1;        // tile of this warpgroup
     const int q = warp & 3;               // TMEM lane quarter this warp may access
     const int r = q * 32 + lane;          // row inside the tile == TMEM lane
@@ -420,9 +439,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // P = exp2(c*s - c*m) as bf16, written over the first 64 columns of this S buffer
       const float mc = (m == -INFINITY) ? 0.f : m * c;
-      // (The MUFU unit, 16 exp2 per clock per SM, needs as long for a 128x128 block as the tensor
-      // core needs for its two contractions; moving a share of the exponentials to an FMA-pipe
-      // polynomial was measured and did not help at this operating point.)
+      // (the MUFU unit, 16 exp2 per clock per SM, needs as long for a 128x128 block as the tensor
+      // core needs for its two contractions at head dimension 128: see exp2_pair)
       float2 rsg[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) rsg[g] = make_float2(0.f, 0.f);
@@ -434,8 +452,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; i += 2) {
             float2 x = fma2(make_float2(__uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1])), make_float2(c, c),
                             make_float2(-mc, -mc));
-            x.x = ex2_approx(x.x);
-            x.y = ex2_approx(x.y);
+            x = exp2_pair<POLY>(g, i >> 1, x);
             rsg[(i >> 1) & 3] = add2(rsg[(i >> 1) & 3], x);
             sr[g][i] = __float_as_uint(x.x);
             sr[g][i + 1] = __float_as_uint(x.y);
@@ -452,8 +469,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; i += 2) {
               float2 x = fma2(make_float2(__uint_as_float(sr[2 * hh + g][i]), __uint_as_float(sr[2 * hh + g][i + 1])),
                               make_float2(c, c), make_float2(-mc, -mc));
-              x.x = ex2_approx(x.x);
-              x.y = ex2_approx(x.y);
+              x = exp2_pair<POLY>(2 * hh + g, i >> 1, x);
               rsg[(i >> 1) & 3] = add2(rsg[(i >> 1) & 3], x);
               pk[16 * g + (i >> 1)] = pack_bf16x2(x.x, x.y);
             }
@@ -488,7 +504,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok && row < p.Sq &&
         bounds_ok(off * (p.out_bf16 ? 2 : 4), static_cast<unsigned long long>(D) * (p.out_bf16 ? 2 : 4), p.o_extent,
                   p.status, p.bounds_detail)) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = l > 1e-30f ? 1.f / l : 0.f;   // a row with no visible key sums to < 2^-100
       if (p.out_bf16) {
         uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.O) + off);
 #pragma unroll
