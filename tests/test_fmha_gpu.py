@@ -217,3 +217,28 @@ def test_row_maximum_that_keeps_growing(cuda_device, growth):
         assert torch.isfinite(got).all()
         assert rel_err(got.cpu().numpy(), want) <= BF16_TOL
     assert ops.last_device_status() == 0
+
+
+@pytest.mark.parametrize("spread", [4.0, 40.0, 400.0])
+def test_wide_logit_spread_head_dimension_64(cuda_device, spread):
+    """bf16, head dimension 64: a fixed share of the exponentials is taken from a cubic on the FMA
+    pipe, which clamps its argument at -125 (2^-125 instead of an underflow to 0).  Scores that
+    lie up to `spread` (natural-log units) below the row maximum, far tails included, must agree
+    with the oracle, row sums and all; masked keys must contribute nothing."""
+    from kernelcodegen_b200 import ops
+
+    b, h, s, d = 1, 2, 512, 64
+    q = torch.zeros((b, h, s, d))
+    q[..., 0] = 1.0
+    k = normal((b, h, s, d), 31) * 0.01
+    k[..., 0] = -torch.rand((b, h, s), generator=torch.Generator().manual_seed(32)) * spread   # the score itself
+    k[:, :, ::37, 0] = 0.0                                                                      # a few keys at the maximum
+    v = normal((b, h, s, d), 33)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    for causal in (False, True):
+        want = oracle.fmha(q.float().numpy(), k.float().numpy(), v.float().numpy(), scale=1.0, causal=causal, threads=0)
+        got = ops.fmha(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), scale=1.0, causal=causal,
+                       out_dtype=torch.float32)
+        assert torch.isfinite(got).all()
+        assert rel_err(got.cpu().numpy(), want) <= BF16_TOL
+    assert ops.last_device_status() == 0
