@@ -315,26 +315,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// 2^x for a pair of arguments on the FMA pipe (no MUFU): x = n + f with n = round(x) taken from the
-// low mantissa bits of x + 1.5 * 2^23, a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5,
-// below bf16 and TF32 rounding), and n added into the exponent field.  The caller clamps
-// x >= -125 so that the exponent stays normal; x may not exceed 127.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c);
-__device__ __forceinline__ float2 add2(float2 a, float2 b);
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  constexpr float MAGIC = 12582912.f;
-  const float2 t = add2(x, make_float2(MAGIC, MAGIC));
-  const float2 n = add2(t, make_float2(-MAGIC, -MAGIC));
-  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = fma2(f, make_float2(0.05517132f, 0.05517132f), make_float2(0.24261054f, 0.24261054f));
-  p = fma2(p, f, make_float2(0.69326097f, 0.69326097f));
-  p = fma2(p, f, make_float2(0.99992812f, 0.99992812f));
-  float2 r;
-  r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
-  r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
-  return r;
-}
-
 // ---- CTA pairs (cluster of 2, tcgen05 cta_group::2) ---------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -433,6 +413,24 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   float2 d;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(pd));
   return d;
+}
+
+// 2^x for a pair of arguments on the FMA pipe (no MUFU): x = n + f with n = round(x) taken from the
+// low mantissa bits of x + 1.5 * 2^23, a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5,
+// below bf16 and TF32 rounding), and n added into the exponent field.  The caller clamps
+// x >= -125 so that the exponent stays normal; x may not exceed 127.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  constexpr float MAGIC = 12582912.f;
+  const float2 t = add2(x, make_float2(MAGIC, MAGIC));
+  const float2 n = add2(t, make_float2(-MAGIC, -MAGIC));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = fma2(f, make_float2(0.05517132f, 0.05517132f), make_float2(0.24261054f, 0.24261054f));
+  p = fma2(p, f, make_float2(0.69326097f, 0.69326097f));
+  p = fma2(p, f, make_float2(0.99992812f, 0.99992812f));
+  float2 r;
+  r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
+  r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
+  return r;
 }
 
 }  // namespace kcg
