@@ -128,7 +128,8 @@ def test_unfused_attention_graph_equals_fused_kernel(cuda_device):
     assert rel_err(o_fused.cpu().numpy(), o_graph.cpu().numpy()) <= 2e-2
 
 
-@pytest.mark.parametrize("shape", [(64, 64), (4096, 1024), (3, 300, 520), (2, 5, 130, 66), (1, 7), (129, 1), (1000, 1002)])
+@pytest.mark.parametrize("shape", [(64, 64), (4096, 1024), (3, 300, 520), (2, 5, 130, 66), (1, 7), (129, 1), (1000, 1002),
+                                   (2, 264, 392), (640, 136)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_transpose_is_exact(cuda_device, shape, dtype):
     """Moves bits only: the result must equal the index-swapped input exactly (vector path for
